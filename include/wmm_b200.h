@@ -1,0 +1,162 @@
+/*
+ * wmm_b200 -- C ABI of the B200 (sm_100a) banded-contraction library.
+ *
+ * This is the native boundary that replaces the reference's pybind module `window_matmul_kernel`
+ * (csrc/window_matmul/window_matmul.cpp:74-106: window_matmul_forward/backward,
+ * unwindow_matmul_forward/backward) and the CUDA launchers behind it
+ * (csrc/window_matmul/cuda/window_matmul_cuda.cu:224-416).  No torch, pybind or C++ types cross it:
+ * device pointers, sizes, element strides, a dtype code and the caller's stream.
+ *
+ * Contract common to every compute entry point
+ *   - All pointers are DEVICE pointers on the CUDA device that is current in the calling thread.
+ *   - The caller owns every buffer (inputs, outputs): the library never allocates, frees or
+ *     synchronises.  Work is enqueued on `stream` (a cudaStream_t passed as void*; NULL = default
+ *     stream) and the call returns at once.
+ *   - Every element of every output is written (out-of-sequence band entries as exact zeros), so
+ *     outputs may be uninitialised memory.  The reference zero-fills its outputs first
+ *     (window_matmul_cuda.cu:242,290-291,338,377-378); that extra pass is not needed here.
+ *   - Return value: WMM_OK or a negative wmm_status; no exception or abort crosses the boundary.
+ *     wmm_last_error_string() gives the reason for the calling thread's last failure.
+ *   - Re-entrant and thread safe; no mutable global state besides the per-thread error string,
+ *     a launch counter and a device-side status word (see wmm_device_status).
+ *
+ * The three primitives.  With W = 2*window+1 and, for a band entry (i, j), the position
+ * p = i + j - window + other_off in the row space of the other operand:
+ *
+ *   band_nt:  Band[b,i,j] = sum_h X[b,i,h] * Y[b,p,h]        if seq_lo <= p < seq_hi, else exactly 0
+ *   band_n :  Out [b,i,h] = sum_{j : seq_lo <= p < seq_hi} Band[b,i,j] * Y[b,p,h]
+ *   band_t :  Out [b,p,h] = sum_{i in [0,rows), 0 <= j <= 2*window} Band[b,i,j] * X[b,i,h]
+ *                           for seq_lo <= p < seq_hi; rows p of Out outside that range are zeros
+ *
+ * X and Band have `rows` rows; Y (band_nt, band_n) and Out of band_t have `other_rows` rows.  The
+ * plain, unsharded operators use other_rows = rows, other_off = 0, seq_lo = 0, seq_hi = rows.  A
+ * sequence-sharded caller passes its local rows plus a halo: other_rows = rows + 2*window,
+ * other_off = window, and seq_lo/seq_hi clip at the ends of the global sequence.
+ *
+ * Arithmetic: products are accumulated in float (double for WMM_F64) and rounded once to the element
+ * type.  For WMM_F32 and WMM_F64 every output element is one sequential chain over the ascending
+ * reduction index, fused multiply-add by default, which is the order of the reference's kernels
+ * (window_matmul_cuda.cu:24-35,64-83); WMM_FLAG_SPLIT_ROUNDING rounds product and sum separately, which
+ * reproduces the reference's CPU loops (cpu/window_matmul_cpu.cpp:43,92-93,137,186-187) bit for bit.
+ */
+#ifndef WMM_B200_H
+#define WMM_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define WMM_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define WMM_API __attribute__((visibility("default")))
+#else
+#define WMM_API
+#endif
+
+typedef enum wmm_dtype { WMM_F16 = 0, WMM_BF16 = 1, WMM_F32 = 2, WMM_F64 = 3 } wmm_dtype;
+
+typedef enum wmm_status {
+  WMM_OK = 0,
+  WMM_ERR_NULL = -1,        /* a required pointer is NULL */
+  WMM_ERR_SHAPE = -2,       /* the reference's "Input mismatch" cases and non-positive sizes */
+  WMM_ERR_DTYPE = -3,       /* unknown dtype code */
+  WMM_ERR_STRIDE = -4,      /* a stride this library cannot address (negative, or overlapping output) */
+  WMM_ERR_TOO_LARGE = -5,   /* an extent or element count beyond the 31-bit / grid limits */
+  WMM_ERR_CUDA = -6,        /* a CUDA runtime/driver call failed; see wmm_last_error_string() */
+  WMM_ERR_UNSUPPORTED = -7, /* a flag combination that no kernel implements */
+  WMM_ERR_DEVICE = -8       /* a kernel gave up on a bounded wait (see wmm_device_status) */
+} wmm_status;
+
+enum {
+  /* fp32/fp64 only: round product and sum separately (bit parity with the reference's CPU loops). */
+  WMM_FLAG_SPLIT_ROUNDING = 1u << 0,
+  /* never take a tensor-core kernel, whatever the shape (testing, and exact fp32 ordering). */
+  WMM_FLAG_FORCE_GENERIC = 1u << 1,
+  /* fail with WMM_ERR_UNSUPPORTED instead of taking the generic kernel (testing the fast path). */
+  WMM_FLAG_REQUIRE_TENSOR = 1u << 2
+};
+
+/* A (batch, rows, cols) operand addressed by ELEMENT strides: either of the two inner strides may be
+ * the unit one, so K of window_matmul can be passed as the (B,N,M) tensor it is
+ * (window_matmul/window_matmul.py:36-37) or as a transposed view of a (B,M,N) tensor, without the
+ * transposing copy of window_matmul_cuda.cu:236. */
+typedef struct wmm_operand {
+  const void *data;
+  int64_t stride_b; /* between batch entries */
+  int64_t stride_r; /* between rows (sequence positions) */
+  int64_t stride_c; /* between columns (hidden features) */
+} wmm_operand;
+
+typedef struct wmm_geometry {
+  int32_t batch;      /* B: batch x heads, flattened */
+  int32_t rows;       /* M: rows of X and of the band */
+  int32_t cols;       /* N: hidden size */
+  int32_t window;     /* w >= 0; the band has 2*w+1 columns */
+  int32_t other_rows; /* rows of Y (band_nt, band_n) / of Out (band_t) */
+  int32_t other_off;  /* position of band entry (i=0, j=window) in that row space */
+  int32_t seq_lo;     /* positions seq_lo <= p < seq_hi are inside the sequence */
+  int32_t seq_hi;
+} wmm_geometry;
+
+/* ---- library / diagnostics ------------------------------------------------------------------- */
+
+/* WMM_ABI_VERSION the library was built with. */
+WMM_API int wmm_version(void);
+/* Reason for the calling thread's most recent non-zero return (never NULL). */
+WMM_API const char *wmm_last_error_string(void);
+/* Static name of a status code. */
+WMM_API const char *wmm_status_string(int status);
+/* Number of kernels this library has launched in this process so far (all threads). */
+WMM_API uint64_t wmm_launch_count(void);
+/* Reads (and, if `clear` is non-zero, resets) the status word that a kernel sets when one of its bounded
+ * waits runs out.  0 = clean.  Synchronises the current device.  Returns the word, or a negative status. */
+WMM_API int64_t wmm_device_status(int clear);
+/* Which kernel family the dispatcher picks for a problem: 0 = generic CUDA-core kernel, 1 = tcgen05
+ * tensor-core kernel.  `primitive` is 1 (band_nt), 2 (band_n) or 3 (band_t); the operands carry the
+ * strides and alignment that decide; pass the same arguments as to the compute call.  Negative = status. */
+WMM_API int wmm_query_path(int primitive, const wmm_operand *a, const wmm_operand *b, const void *band,
+                   const wmm_geometry *g, int dtype, unsigned flags);
+
+/* ---- the three primitives --------------------------------------------------------------------- */
+
+/* Band = band(X * Y^T): replaces the kernel window_matmul_kernel (window_matmul_cuda.cu:37-91), used by
+ * window_matmul_fw_cuda (:224-270; X=Q, Y=K^T) and for grad_A in unwindow_matmul_bw_cuda (:403-408;
+ * X=grad_O, Y=V).  `band` is a contiguous (batch, rows, 2w+1) output. */
+WMM_API int wmm_band_nt(const wmm_operand *x, const wmm_operand *y, void *band, const wmm_geometry *g, int dtype,
+                unsigned flags, void *stream);
+
+/* Out = unskew(Band) * Y: replaces unwindow_matmul_kernel_A (window_matmul_cuda.cu:93-156), used by
+ * unwindow_matmul_fw_cuda (:321-358; Y=V) and for grad_Q in window_matmul_bw_cuda (:308-312; Band=grad_A,
+ * Y=K^T).  `band` is a contiguous (batch, rows, 2w+1) input; `out` is written through its strides. */
+WMM_API int wmm_band_n(const void *band, const wmm_operand *y, const wmm_operand *out, const wmm_geometry *g,
+               int dtype, unsigned flags, void *stream);
+
+/* Out = unskew(Band)^T * X: replaces unwindow_matmul_kernel_B (window_matmul_cuda.cu:158-222), used for
+ * grad_K in window_matmul_bw_cuda (:313-317; Band=grad_A, X=Q) and grad_V in unwindow_matmul_bw_cuda
+ * (:409-414; Band=A, X=grad_O).  Out has g->other_rows rows. */
+WMM_API int wmm_band_t(const void *band, const wmm_operand *x, const wmm_operand *out, const wmm_geometry *g,
+               int dtype, unsigned flags, void *stream);
+
+/* ---- the two backward passes ------------------------------------------------------------------- */
+
+/* grad_Q = band_n(grad_A, K^T), grad_K^T = band_t(grad_A, Q): replaces window_matmul_bw_cuda
+ * (window_matmul_cuda.cu:272-319).  kt / grad_kt are K and grad_K in (batch, rows, cols) index order
+ * (pass a (B,N,M) tensor with its two inner strides swapped).  Plain geometry only
+ * (other_rows = rows, other_off = 0); sharded callers use the primitives. */
+WMM_API int wmm_window_bwd(const wmm_operand *q, const wmm_operand *kt, const void *grad_band,
+                   const wmm_operand *grad_q, const wmm_operand *grad_kt, const wmm_geometry *g, int dtype,
+                   unsigned flags, void *stream);
+
+/* grad_A = band_nt(grad_O, V), grad_V = band_t(A, grad_O): replaces unwindow_matmul_bw_cuda
+ * (window_matmul_cuda.cu:360-416).  Plain geometry only. */
+WMM_API int wmm_unwindow_bwd(const void *band, const wmm_operand *v, const wmm_operand *grad_o, void *grad_band,
+                     const wmm_operand *grad_v, const wmm_geometry *g, int dtype, unsigned flags,
+                     void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WMM_B200_H */

@@ -1,0 +1,270 @@
+// The C ABI (include/wmm_b200.h): argument validation, kernel-family dispatch, error reporting.
+// Nothing here allocates device memory or synchronises, except wmm_device_status().
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+
+#include "wmm_common.cuh"
+
+namespace {
+
+thread_local char tls_error[512] = "no error";
+std::atomic<uint64_t> g_launches{0};
+
+int fail(int status, const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(tls_error, sizeof(tls_error), fmt, ap);
+  va_end(ap);
+  return status;
+}
+
+size_t elem_size(int dtype) {
+  switch (dtype) {
+    case WMM_F16:
+    case WMM_BF16: return 2;
+    case WMM_F32: return 4;
+    case WMM_F64: return 8;
+    default: return 0;
+  }
+}
+
+int check_geometry(const wmm_geometry *g, int dtype, unsigned flags) {
+  if (!g) return fail(WMM_ERR_NULL, "geometry is NULL");
+  if (elem_size(dtype) == 0) return fail(WMM_ERR_DTYPE, "unknown dtype code %d", dtype);
+  if (g->batch < 0 || g->rows < 0 || g->cols < 0 || g->other_rows < 0 || g->window < 0)
+    return fail(WMM_ERR_SHAPE, "Input mismatch: negative extent (batch %d rows %d cols %d other_rows %d window %d)",
+                g->batch, g->rows, g->cols, g->other_rows, g->window);
+  if (g->seq_lo < 0 || g->seq_lo > g->seq_hi || g->seq_hi > g->other_rows)
+    return fail(WMM_ERR_SHAPE, "Input mismatch: sequence range [%d,%d) not inside [0,%d)", g->seq_lo, g->seq_hi,
+                g->other_rows);
+  if (g->window > (1 << 28) || (int64_t)g->rows + 2ll * g->window + 256 > 0x7fffffffLL ||
+      (int64_t)g->other_rows + 2ll * g->window + 256 > 0x7fffffffLL ||
+      (int64_t)(g->other_off < 0 ? -(int64_t)g->other_off : g->other_off) > (1ll << 30))
+    return fail(WMM_ERR_TOO_LARGE, "extent beyond the 31-bit index range");
+  if ((flags & WMM_FLAG_FORCE_GENERIC) && (flags & WMM_FLAG_REQUIRE_TENSOR))
+    return fail(WMM_ERR_UNSUPPORTED, "FORCE_GENERIC and REQUIRE_TENSOR exclude each other");
+  if ((flags & WMM_FLAG_SPLIT_ROUNDING) && (flags & WMM_FLAG_REQUIRE_TENSOR))
+    return fail(WMM_ERR_UNSUPPORTED, "split rounding exists only in the CUDA-core kernels");
+  return WMM_OK;
+}
+
+int check_operand(const wmm_operand *op, const char *name, bool is_output, bool empty) {
+  if (!op) return fail(WMM_ERR_NULL, "operand %s is NULL", name);
+  if (!op->data && !empty) return fail(WMM_ERR_NULL, "operand %s has a NULL data pointer", name);
+  if (op->stride_b < 0 || op->stride_r < 0 || op->stride_c < 0)
+    return fail(WMM_ERR_STRIDE, "operand %s has a negative stride", name);
+  if (is_output && (op->stride_r == 0 || op->stride_c == 0) && !empty)
+    return fail(WMM_ERR_STRIDE, "output %s has a zero stride (overlapping elements)", name);
+  return WMM_OK;
+}
+
+void fill(wmm::Problem &p, const wmm_geometry *g, int dtype, unsigned flags) {
+  p.B = g->batch;
+  p.M = g->rows;
+  p.N = g->cols;
+  p.w = g->window;
+  p.Mo = g->other_rows;
+  p.off = g->other_off;
+  p.lo = g->seq_lo;
+  p.hi = g->seq_hi;
+  p.dtype = dtype;
+  p.flags = flags;
+}
+
+void set_a(wmm::Problem &p, const wmm_operand *x) {
+  p.a = x->data;
+  p.a_sb = x->stride_b;
+  p.a_sr = x->stride_r;
+  p.a_sc = x->stride_c;
+}
+void set_b(wmm::Problem &p, const wmm_operand *x) {
+  p.b = x->data;
+  p.b_sb = x->stride_b;
+  p.b_sr = x->stride_r;
+  p.b_sc = x->stride_c;
+}
+void set_o(wmm::Problem &p, const wmm_operand *x) {
+  p.o = const_cast<void *>(x->data);
+  p.o_sb = x->stride_b;
+  p.o_sr = x->stride_r;
+  p.o_sc = x->stride_c;
+}
+void set_band_a(wmm::Problem &p, const void *band) {
+  p.a = band;
+  p.a_sb = p.a_sr = p.a_sc = 0;
+}
+void set_band_o(wmm::Problem &p, void *band) {
+  p.o = band;
+  p.o_sb = p.o_sr = p.o_sc = 0;
+}
+
+bool wants_tensor(wmm::Primitive prim, const wmm::Problem &p) {
+  if (p.flags & (WMM_FLAG_FORCE_GENERIC | WMM_FLAG_SPLIT_ROUNDING)) return false;
+  return wmm::tensor_eligible(prim, p);
+}
+
+int dispatch(wmm::Primitive prim, const wmm::Problem &p, void *stream) {
+  const bool tensor = wants_tensor(prim, p);
+  if (!tensor && (p.flags & WMM_FLAG_REQUIRE_TENSOR))
+    return fail(WMM_ERR_UNSUPPORTED, "no tensor-core kernel takes this problem (primitive %d)", (int)prim);
+  int launches = 0;
+  cudaError_t e = tensor ? wmm::launch_tensor(prim, p, (cudaStream_t)stream, &launches)
+                         : wmm::launch_generic(prim, p, (cudaStream_t)stream, &launches);
+  g_launches.fetch_add((uint64_t)launches, std::memory_order_relaxed);
+  if (e != cudaSuccess)
+    return fail(WMM_ERR_CUDA, "CUDA error launching primitive %d: %s", (int)prim, cudaGetErrorString(e));
+  return WMM_OK;
+}
+
+// Problems with no output element need no launch; outputs with elements but an empty reduction are
+// handled by the kernels (they write zeros).
+bool nothing_to_write(wmm::Primitive prim, const wmm_geometry *g) {
+  if (g->batch == 0 || g->cols == 0 && prim != wmm::BAND_NT) return true;
+  if (prim == wmm::BAND_T) return g->other_rows == 0;
+  return g->rows == 0;
+}
+
+int build(wmm::Primitive prim, wmm::Problem &p, const wmm_operand *x, const wmm_operand *y, const void *band_in,
+          void *band_out, const wmm_operand *out, const wmm_geometry *g, int dtype, unsigned flags) {
+  if (int s = check_geometry(g, dtype, flags)) return s;
+  const bool empty = nothing_to_write(prim, g);
+  fill(p, g, dtype, flags);
+  switch (prim) {
+    case wmm::BAND_NT:
+      if (int s = check_operand(x, "x", false, empty || g->cols == 0)) return s;
+      if (int s = check_operand(y, "y", false, empty || g->cols == 0 || g->other_rows == 0)) return s;
+      if (!band_out && !empty) return fail(WMM_ERR_NULL, "band output is NULL");
+      set_a(p, x);
+      set_b(p, y);
+      set_band_o(p, band_out);
+      break;
+    case wmm::BAND_N:
+      if (!band_in && !empty) return fail(WMM_ERR_NULL, "band input is NULL");
+      if (int s = check_operand(y, "y", false, empty || g->other_rows == 0)) return s;
+      if (int s = check_operand(out, "out", true, empty)) return s;
+      set_band_a(p, band_in);
+      set_b(p, y);
+      set_o(p, out);
+      break;
+    default:
+      if (!band_in && !empty && g->rows > 0) return fail(WMM_ERR_NULL, "band input is NULL");
+      if (int s = check_operand(x, "x", false, empty || g->rows == 0)) return s;
+      if (int s = check_operand(out, "out", true, empty)) return s;
+      set_band_a(p, band_in);
+      set_b(p, x);
+      set_o(p, out);
+      break;
+  }
+  return empty ? 1 : WMM_OK;  // 1: valid, nothing to do
+}
+
+int plain_geometry(const wmm_geometry *g) {
+  if (g && (g->other_rows != g->rows || g->other_off != 0))
+    return fail(WMM_ERR_SHAPE, "Input mismatch: the fused backward entry points take the plain geometry only");
+  return WMM_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int wmm_version(void) { return WMM_ABI_VERSION; }
+
+const char *wmm_last_error_string(void) { return tls_error; }
+
+const char *wmm_status_string(int status) {
+  switch (status) {
+    case WMM_OK: return "WMM_OK";
+    case WMM_ERR_NULL: return "WMM_ERR_NULL";
+    case WMM_ERR_SHAPE: return "WMM_ERR_SHAPE";
+    case WMM_ERR_DTYPE: return "WMM_ERR_DTYPE";
+    case WMM_ERR_STRIDE: return "WMM_ERR_STRIDE";
+    case WMM_ERR_TOO_LARGE: return "WMM_ERR_TOO_LARGE";
+    case WMM_ERR_CUDA: return "WMM_ERR_CUDA";
+    case WMM_ERR_UNSUPPORTED: return "WMM_ERR_UNSUPPORTED";
+    case WMM_ERR_DEVICE: return "WMM_ERR_DEVICE";
+    default: return "WMM_ERR_UNKNOWN";
+  }
+}
+
+uint64_t wmm_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int64_t wmm_device_status(int clear) {
+  unsigned long long word = 0;
+  cudaError_t e = wmm::read_device_status(&word, clear != 0);
+  if (e != cudaSuccess) return fail(WMM_ERR_CUDA, "reading the device status word: %s", cudaGetErrorString(e));
+  return (int64_t)word;
+}
+
+int wmm_query_path(int primitive, const wmm_operand *a, const wmm_operand *b, const void *band,
+                   const wmm_geometry *g, int dtype, unsigned flags) {
+  wmm::Problem p{};
+  int s;
+  switch (primitive) {
+    case wmm::BAND_NT: s = build(wmm::BAND_NT, p, a, b, nullptr, const_cast<void *>(band), nullptr, g, dtype, flags); break;
+    case wmm::BAND_N: s = build(wmm::BAND_N, p, nullptr, a, band, nullptr, b, g, dtype, flags); break;
+    case wmm::BAND_T: s = build(wmm::BAND_T, p, a, nullptr, band, nullptr, b, g, dtype, flags); break;
+    default: return fail(WMM_ERR_UNSUPPORTED, "unknown primitive %d", primitive);
+  }
+  if (s < 0) return s;
+  if (s == 1) return 0;
+  return wants_tensor((wmm::Primitive)primitive, p) ? 1 : 0;
+}
+
+int wmm_band_nt(const wmm_operand *x, const wmm_operand *y, void *band, const wmm_geometry *g, int dtype,
+                unsigned flags, void *stream) {
+  wmm::Problem p{};
+  const int s = build(wmm::BAND_NT, p, x, y, nullptr, band, nullptr, g, dtype, flags);
+  if (s != WMM_OK) return s < 0 ? s : WMM_OK;
+  return dispatch(wmm::BAND_NT, p, stream);
+}
+
+int wmm_band_n(const void *band, const wmm_operand *y, const wmm_operand *out, const wmm_geometry *g, int dtype,
+               unsigned flags, void *stream) {
+  wmm::Problem p{};
+  const int s = build(wmm::BAND_N, p, nullptr, y, band, nullptr, out, g, dtype, flags);
+  if (s != WMM_OK) return s < 0 ? s : WMM_OK;
+  return dispatch(wmm::BAND_N, p, stream);
+}
+
+int wmm_band_t(const void *band, const wmm_operand *x, const wmm_operand *out, const wmm_geometry *g, int dtype,
+               unsigned flags, void *stream) {
+  wmm::Problem p{};
+  const int s = build(wmm::BAND_T, p, x, nullptr, band, nullptr, out, g, dtype, flags);
+  if (s != WMM_OK) return s < 0 ? s : WMM_OK;
+  return dispatch(wmm::BAND_T, p, stream);
+}
+
+int wmm_window_bwd(const wmm_operand *q, const wmm_operand *kt, const void *grad_band, const wmm_operand *grad_q,
+                   const wmm_operand *grad_kt, const wmm_geometry *g, int dtype, unsigned flags, void *stream) {
+  if (int s = plain_geometry(g)) return s;
+  // validate both halves before launching either, so a bad argument never leaves half a result
+  wmm::Problem pq{}, pk{};
+  const int sq = build(wmm::BAND_N, pq, nullptr, kt, grad_band, nullptr, grad_q, g, dtype, flags);
+  if (sq < 0) return sq;
+  const int sk = build(wmm::BAND_T, pk, q, nullptr, grad_band, nullptr, grad_kt, g, dtype, flags);
+  if (sk < 0) return sk;
+  if (sq == WMM_OK)
+    if (int s = dispatch(wmm::BAND_N, pq, stream)) return s;
+  if (sk == WMM_OK)
+    if (int s = dispatch(wmm::BAND_T, pk, stream)) return s;
+  return WMM_OK;
+}
+
+int wmm_unwindow_bwd(const void *band, const wmm_operand *v, const wmm_operand *grad_o, void *grad_band,
+                     const wmm_operand *grad_v, const wmm_geometry *g, int dtype, unsigned flags, void *stream) {
+  if (int s = plain_geometry(g)) return s;
+  wmm::Problem pa{}, pv{};
+  const int sa = build(wmm::BAND_NT, pa, grad_o, v, nullptr, grad_band, nullptr, g, dtype, flags);
+  if (sa < 0) return sa;
+  const int sv = build(wmm::BAND_T, pv, grad_o, nullptr, band, nullptr, grad_v, g, dtype, flags);
+  if (sv < 0) return sv;
+  if (sa == WMM_OK)
+    if (int s = dispatch(wmm::BAND_NT, pa, stream)) return s;
+  if (sv == WMM_OK)
+    if (int s = dispatch(wmm::BAND_T, pv, stream)) return s;
+  return WMM_OK;
+}
+
+}  // extern "C"

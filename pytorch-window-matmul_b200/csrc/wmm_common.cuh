@@ -1,0 +1,65 @@
+// Shared declarations of the banded-contraction kernels (internal; the public surface is include/wmm_b200.h).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/wmm_b200.h"
+
+namespace wmm {
+
+// One banded contraction, after validation.  `a` is the first operand in the order of the public
+// entry point (X for band_nt, the band for band_n / band_t), `b` the second, `o` the output.  The band
+// is always contiguous (batch, rows, 2w+1) and carries no strides.
+struct Problem {
+  const void *a;
+  const void *b;
+  void *o;
+  int64_t a_sb, a_sr, a_sc;
+  int64_t b_sb, b_sr, b_sc;
+  int64_t o_sb, o_sr, o_sc;
+  int32_t B, M, N, w;      // batch, rows of X / band, hidden size, window
+  int32_t Mo, off, lo, hi; // rows of the other row space, its offset, in-sequence range
+  int32_t dtype;
+  uint32_t flags;
+};
+
+enum Primitive { BAND_NT = 1, BAND_N = 2, BAND_T = 3 };
+
+// Launchers.  Each returns cudaSuccess or the launch error; `launches` is incremented per kernel.
+cudaError_t launch_generic(Primitive prim, const Problem &p, cudaStream_t stream, int *launches);
+
+// Tensor-core (tcgen05) family: `eligible` is a pure host-side predicate on shape, dtype, strides and
+// alignment; `launch_tensor` must only be called when it holds.
+bool tensor_eligible(Primitive prim, const Problem &p);
+cudaError_t launch_tensor(Primitive prim, const Problem &p, cudaStream_t stream, int *launches);
+
+// Device-side status word: a kernel that abandons a bounded wait ORs a code into it.  Synchronises the
+// current device, copies the word out and optionally clears it.
+cudaError_t read_device_status(unsigned long long *word, bool clear);
+
+template <typename T> struct ElemTraits;
+template <> struct ElemTraits<float> {
+  using Acc = float;
+  static __device__ __forceinline__ float load(const float *p) { return *p; }
+  static __device__ __forceinline__ float store(float v) { return v; }
+};
+template <> struct ElemTraits<double> {
+  using Acc = double;
+  static __device__ __forceinline__ double load(const double *p) { return *p; }
+  static __device__ __forceinline__ double store(double v) { return v; }
+};
+template <> struct ElemTraits<__half> {
+  using Acc = float;
+  static __device__ __forceinline__ float load(const __half *p) { return __half2float(*p); }
+  static __device__ __forceinline__ __half store(float v) { return __float2half_rn(v); }
+};
+template <> struct ElemTraits<__nv_bfloat16> {
+  using Acc = float;
+  static __device__ __forceinline__ float load(const __nv_bfloat16 *p) { return __bfloat162float(*p); }
+  static __device__ __forceinline__ __nv_bfloat16 store(float v) { return __float2bfloat16_rn(v); }
+};
+
+}  // namespace wmm

@@ -1,0 +1,88 @@
+"""CPU-side checks of the native boundary: the library loads, exports every symbol the public header
+declares, and validates arguments without touching a GPU."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "wmm_b200.h")
+
+
+def _declared():
+    text = open(HEADER).read()
+    return sorted(set(re.findall(r"WMM_API\s+[\w\s\*]+?\b(wmm_\w+)\s*\(", text)))
+
+
+def test_header_declares_the_expected_entry_points():
+    names = _declared()
+    for n in ("wmm_band_nt", "wmm_band_n", "wmm_band_t", "wmm_window_bwd", "wmm_unwindow_bwd", "wmm_version",
+              "wmm_last_error_string"):
+        assert n in names
+
+
+def test_library_exports_every_declared_symbol():
+    from window_matmul import _native as N
+
+    lib = ctypes.CDLL(N.LIB_PATH)
+    for name in _declared():
+        assert hasattr(lib, name), name
+    assert lib.wmm_version() == 1
+
+
+def test_argument_validation_needs_no_gpu():
+    from window_matmul import _native as N
+
+    g = N.geometry(2, 8, 4, 2)
+    op = N.Operand(0, 0, 0, 0)
+    # NULL data pointers
+    assert N.lib.wmm_band_nt(op, op, None, g, N.F32, 0, None) == -1
+    assert b"NULL" in N.lib.wmm_last_error_string()
+    # unknown dtype
+    ok = N.Operand(256, 32, 4, 1)
+    assert N.lib.wmm_band_nt(ok, ok, 256, g, 17, 0, None) == -3
+    # sequence range outside the other operand's rows
+    bad = N.geometry(2, 8, 4, 2, other_rows=8, seq=(0, 9))
+    assert N.lib.wmm_band_n(256, ok, ok, bad, N.F32, 0, None) == -2
+    assert b"Input mismatch" in N.lib.wmm_last_error_string()
+    # negative window
+    assert N.lib.wmm_band_t(256, ok, ok, N.geometry(2, 8, 4, -1), N.F32, 0, None) == -2
+    # overlapping output
+    assert N.lib.wmm_band_n(256, ok, N.Operand(256, 32, 0, 1), g, N.F32, 0, None) == -4
+    # contradictory flags
+    assert N.lib.wmm_band_nt(ok, ok, 256, g, N.F32, N.FLAG_FORCE_GENERIC | N.FLAG_REQUIRE_TENSOR, None) == -7
+    # the fused backward entry points take the plain geometry only
+    sharded = N.geometry(2, 8, 4, 2, other_rows=12, other_off=2)
+    assert N.lib.wmm_window_bwd(ok, ok, 256, ok, ok, sharded, N.F32, 0, None) == -2
+    # empty problems succeed without a launch
+    before = N.launch_count()
+    assert N.lib.wmm_band_nt(op, op, None, N.geometry(0, 8, 4, 2), N.F32, 0, None) == 0
+    assert N.launch_count() == before
+    assert N.lib.wmm_status_string(-6) == b"WMM_ERR_CUDA"
+
+
+def test_python_surface_matches_the_reference():
+    import inspect
+
+    import window_matmul as wm
+
+    assert wm.__all__ == ["window_matmul", "unwindow_matmul"]
+    for fn in (wm.window_matmul, wm.unwindow_matmul):
+        assert list(inspect.signature(fn).parameters) == ["inp", "other", "window_size"]
+
+
+def test_cpu_tensors_are_refused_loudly():
+    import torch
+
+    import window_matmul as wm
+
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        wm.window_matmul(torch.randn(2, 4, 3), torch.randn(2, 3, 4), 1)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        wm.unwindow_matmul(torch.randn(2, 4, 3), torch.randn(2, 4, 3), 1)
+    # window_size == 0 never reaches the kernels (window_matmul/window_matmul.py:33-34, 69-70 of the reference)
+    q, k = torch.randn(2, 4, 3), torch.randn(2, 3, 4)
+    assert wm.window_matmul(q, k, 0).shape == (2, 4, 1)
+    a, v = torch.randn(2, 4, 1), torch.randn(2, 4, 3)
+    assert torch.equal(wm.unwindow_matmul(a, v, 0), a * v)
