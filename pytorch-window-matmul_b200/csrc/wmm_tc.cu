@@ -1,6 +1,22 @@
-// tcgen05 / TMA kernels for the banded contractions (16-bit inputs).  Placeholder until the kernels land:
-// nothing is eligible, so every problem takes the CUDA-core family.
+// tcgen05 / TMA kernels for the banded contractions on 16-bit inputs (fp16, bf16; fp32 accumulation in TMEM).
+//
+// Geometry shared by the three kernels.  A CTA owns tiles of 128 band rows.  In dense (row i, position p)
+// coordinates a tile touches positions p0 .. p0 + 128 + 2w - 1, processed in chunks of 128.  The band
+// tensor is contiguous (B, M, 2w+1); entry (i, j) sits at element i*(2w+1) + j = i*2w + (i + j) of its
+// batch, so the band IS a dense row-major matrix with row pitch 2w (not 2w+1) in the coordinates
+// (row i, x = i + j): a (128 rows x 128 positions) block of the dense product is a plain pitched 2-D
+// box of the band tensor.  That makes band tiles TMA-addressable (3-D map: x, row, batch) although the
+// true row length 2w+1 is odd; elements of a box outside 0 <= j <= 2w alias entries of neighbouring
+// rows, so only boxes that lie wholly inside the band are moved by TMA, and the two triangular ends of
+// a tile are moved with predicated vector accesses.
+//
+// Warp roles (persistent CTAs, one per SM, tiles taken round-robin with the sequence index fastest so
+// that neighbouring CTAs share their halo rows in L2): warp 0 = TMA producer, warp 1 = MMA issuer and
+// TMEM owner, warps 2-5 = epilogue (TMEM -> registers -> global / staging + TMA store).
+#include <mutex>
+
 #include "wmm_common.cuh"
+#include "wmm_ptx.cuh"
 
 namespace wmm {
 
@@ -16,8 +32,421 @@ cudaError_t read_device_status(unsigned long long *word, bool clear) {
   return e;
 }
 
-bool tensor_eligible(Primitive, const Problem &) { return false; }
+namespace {
 
-cudaError_t launch_tensor(Primitive, const Problem &, cudaStream_t, int *) { return cudaErrorNotSupported; }
+using namespace ptx;
+
+constexpr int TILE = 128;       // band rows per tile = MMA M
+constexpr int CHUNK = 128;      // positions per chunk = MMA N of band_nt
+constexpr int ACC_STAGES = 4;   // 4 x 128 TMEM columns
+constexpr int NT_THREADS = 192;
+constexpr int EPI_THREADS = 128;
+constexpr uint32_t EPI_BAR = 1;
+
+// Status codes OR-ed into g_device_status when a bounded wait runs out.
+constexpr unsigned long long ST_NT_TIMEOUT = 1ull << 0;
+
+// A (128 rows x NH) 16-bit operand tile in shared memory, K-major, written by TMA with the hardware
+// swizzle and read by tcgen05.mma through a matching descriptor.  Rows are SW_BYTES long; wider tiles
+// are split into boxes of 64 columns.
+template <int NH> struct KMajorTile {
+  static constexpr int BOXK = NH >= 64 ? 64 : NH;
+  static constexpr int SW_BYTES = BOXK * 2;
+  static constexpr int NBOX = NH / BOXK;
+  static constexpr int BOX_BYTES = 128 * SW_BYTES;
+  static constexpr int BYTES = NBOX * BOX_BYTES;
+  static constexpr uint32_t SWZ_CODE = SW_BYTES == 128 ? 2u : SW_BYTES == 64 ? 4u : 6u;
+  static constexpr int KSTEPS = NH / 16;
+  static constexpr uint64_t DESC = smem_desc_base(16, 8 * SW_BYTES, SWZ_CODE);
+  static __device__ __forceinline__ uint32_t kstep_offset(int ks) {
+    return (uint32_t)((ks * 16 / BOXK) * BOX_BYTES + (ks * 16 % BOXK) * 2);
+  }
+};
+
+template <bool BF16> __device__ __forceinline__ uint32_t pack2(uint32_t lo_bits, uint32_t hi_bits) {
+  const float lo = __uint_as_float(lo_bits), hi = __uint_as_float(hi_bits);
+  if (BF16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+  } else {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+  }
+}
+template <bool BF16> __device__ __forceinline__ uint16_t pack1(uint32_t bits) {
+  const float f = __uint_as_float(bits);
+  if (BF16) {
+    __nv_bfloat16 v = __float2bfloat16_rn(f);
+    return *reinterpret_cast<uint16_t *>(&v);
+  } else {
+    __half v = __float2half_rn(f);
+    return *reinterpret_cast<uint16_t *>(&v);
+  }
+}
+
+struct NtParams {
+  int B, M, w, off, lo, hi;
+  int tiles_per_batch, total_tiles, nchunks;
+  void *band;
+};
+
+template <int NH> struct NtSmem {
+  using OT = KMajorTile<NH>;
+  static constexpr int QS = 2;
+  static constexpr int KS = NH >= 128 ? 2 : 4;
+  static constexpr int STAGE_HALF = TILE * 128;  // 128 rows x 64 columns x 2 bytes
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = OFF_Q + QS * OT::BYTES;
+  static constexpr int OFF_STAGE = OFF_K + KS * OT::BYTES;
+  static constexpr int OFF_BARS = OFF_STAGE + 2 * 2 * STAGE_HALF;
+  static constexpr int NBARS = 2 * QS + 2 * KS + 2 * ACC_STAGES;
+  static constexpr int OFF_MISC = OFF_BARS + NBARS * 8;
+  static constexpr int BYTES = OFF_MISC + 32;
+  static constexpr int ALLOC = BYTES + 1024;  // slack to align the base to 1024 B
+};
+
+// band_nt: Band = band(X Y^T).  One MMA chunk = X tile (128 x NH) times 128 rows of Y.
+template <bool BF16, int NH>
+__global__ void __launch_bounds__(NT_THREADS, 1)
+band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
+                  const __grid_constant__ CUtensorMap map_band, const NtParams p) {
+  using S = NtSmem<NH>;
+  using OT = KMajorTile<NH>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t *base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bars = base + S::OFF_BARS;
+  auto bar_q_full = [&](int s) { return bars + 8u * s; };
+  auto bar_q_empty = [&](int s) { return bars + 8u * (S::QS + s); };
+  auto bar_k_full = [&](int s) { return bars + 8u * (2 * S::QS + s); };
+  auto bar_k_empty = [&](int s) { return bars + 8u * (2 * S::QS + S::KS + s); };
+  auto bar_acc_full = [&](int s) { return bars + 8u * (2 * S::QS + 2 * S::KS + s); };
+  auto bar_acc_empty = [&](int s) { return bars + 8u * (2 * S::QS + 2 * S::KS + ACC_STAGES + s); };
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + S::OFF_MISC);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(base_ptr + S::OFF_MISC + 4);
+  volatile int *epi_ok = reinterpret_cast<volatile int *>(base_ptr + S::OFF_MISC + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S::QS; s++) { mbar_init(bar_q_full(s), 1); mbar_init(bar_q_empty(s), 1); }
+    for (int s = 0; s < S::KS; s++) { mbar_init(bar_k_full(s), 1); mbar_init(bar_k_empty(s), 1); }
+    for (int s = 0; s < ACC_STAGES; s++) { mbar_init(bar_acc_full(s), 1); mbar_init(bar_acc_empty(s), EPI_THREADS); }
+    *abort_flag = 0;
+    *epi_ok = 1;
+    fence_mbar_init();
+    prefetch_tmap(&map_x);
+    prefetch_tmap(&map_y);
+    prefetch_tmap(&map_band);
+  }
+  if (warp == 1) {
+    tmem_alloc(base + S::OFF_MISC, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int qit = 0, kit = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x, ++qit) {
+        const int b = tile / p.tiles_per_batch, r0 = (tile % p.tiles_per_batch) * TILE;
+        const int qs = qit % S::QS;
+        if (!(ok = mbar_wait(bar_q_empty(qs), ((qit / S::QS) & 1) ^ 1, abort_flag))) break;
+        mbar_expect_tx(bar_q_full(qs), OT::BYTES);
+#pragma unroll
+        for (int bx = 0; bx < OT::NBOX; bx++)
+          tma_load_3d(base + S::OFF_Q + qs * OT::BYTES + bx * OT::BOX_BYTES, &map_x, bar_q_full(qs), bx * OT::BOXK, r0, b);
+        for (int c = 0; c < p.nchunks; ++c, ++kit) {
+          const int ks = kit % S::KS;
+          if (!(ok = mbar_wait(bar_k_empty(ks), ((kit / S::KS) & 1) ^ 1, abort_flag))) break;
+          mbar_expect_tx(bar_k_full(ks), OT::BYTES);
+          const int p0 = r0 - p.w + p.off + c * CHUNK;
+#pragma unroll
+          for (int bx = 0; bx < OT::NBOX; bx++)
+            tma_load_3d(base + S::OFF_K + ks * OT::BYTES + bx * OT::BOX_BYTES, &map_y, bar_k_full(ks), bx * OT::BOXK, p0, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t IDESC = instr_desc_f16(BF16, false, false, TILE, CHUNK);
+      int qit = 0, kit = 0, ait = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x, ++qit) {
+        const int qs = qit % S::QS;
+        if (!(ok = mbar_wait(bar_q_full(qs), (qit / S::QS) & 1, abort_flag))) break;
+        const uint32_t q_addr = base + S::OFF_Q + qs * OT::BYTES;
+        for (int c = 0; c < p.nchunks; ++c, ++kit, ++ait) {
+          const int ks = kit % S::KS, as = ait % ACC_STAGES;
+          if (!(ok = mbar_wait(bar_k_full(ks), (kit / S::KS) & 1, abort_flag))) break;
+          if (!(ok = mbar_wait(bar_acc_empty(as), ((ait / ACC_STAGES) & 1) ^ 1, abort_flag))) break;
+          tc_fence_after_sync();
+          const uint32_t k_addr = base + S::OFF_K + ks * OT::BYTES;
+#pragma unroll
+          for (int s = 0; s < OT::KSTEPS; s++)
+            umma_f16(tmem_base + as * CHUNK, smem_desc(OT::DESC, q_addr + OT::kstep_offset(s)),
+                     smem_desc(OT::DESC, k_addr + OT::kstep_offset(s)), IDESC, s > 0 ? 1u : 0u);
+          umma_commit(bar_k_empty(ks));
+          umma_commit(bar_acc_full(as));
+        }
+        if (ok) umma_commit(bar_q_empty(qs));
+      }
+    }
+  } else {
+    // ---------------- epilogue: 128 threads, thread <-> band row of the tile ----------------
+    const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 belong to this warp
+    const int rr = quarter * 32 + lane;
+    const int epi_tid = threadIdx.x - 64;
+    const int W = 2 * p.w + 1;
+    uint16_t *band = static_cast<uint16_t *>(p.band);
+    int ait = 0, sit = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
+      const int b = tile / p.tiles_per_batch, r0 = (tile % p.tiles_per_batch) * TILE;
+      const int i = r0 + rr;
+      for (int c = 0; c < p.nchunks; ++c, ++ait) {
+        const int as = ait % ACC_STAGES;
+        const bool full = (c >= 1) && (c * CHUNK + CHUNK - 1 <= 2 * p.w);
+        const int sb = sit & 1;
+        if (epi_tid == 0) {
+          int good = mbar_wait(bar_acc_full(as), (ait / ACC_STAGES) & 1, abort_flag) ? 1 : 0;
+          if (full) bulk_wait_read<1>();  // the store that last read staging buffer `sb` has drained
+          *epi_ok = good;
+        }
+        named_bar_sync(EPI_BAR, EPI_THREADS);
+        if (!(ok = (*epi_ok != 0))) break;
+        tc_fence_after_sync();
+        const uint32_t taddr = tmem_base + as * CHUNK + ((uint32_t)(quarter * 32) << 16);
+        // positions of this chunk that lie inside the sequence: kk in [kk_lo, kk_hi)
+        const int p0 = r0 - p.w + p.off + c * CHUNK;
+        const int kk_lo = p.lo - p0, kk_hi = p.hi - p0;
+        const bool edge = kk_lo > 0 || kk_hi < CHUNK;
+        if (full) {
+          const uint32_t stage = base + S::OFF_STAGE + sb * 2 * S::STAGE_HALF;
+#pragma unroll
+          for (int g = 0; g < 4; g++) {
+            uint32_t v[32];
+            tmem_ld_x32(taddr + g * 32, v);
+            tmem_ld_wait();
+            if (edge) {
+#pragma unroll
+              for (int e = 0; e < 32; e++) {
+                const int kk = g * 32 + e;
+                if (kk < kk_lo || kk >= kk_hi) v[e] = 0u;
+              }
+            }
+            const uint32_t half_base = stage + (g >> 1) * S::STAGE_HALF + rr * 128;
+#pragma unroll
+            for (int q4 = 0; q4 < 4; q4++) {
+              const int cc = (g & 1) * 4 + q4;  // 16-byte column of the 128-byte staging row
+              const uint32_t a = half_base + ((cc ^ (rr & 7)) << 4);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(pack2<BF16>(v[q4 * 8 + 0], v[q4 * 8 + 1])),
+                           "r"(pack2<BF16>(v[q4 * 8 + 2], v[q4 * 8 + 3])), "r"(pack2<BF16>(v[q4 * 8 + 4], v[q4 * 8 + 5])),
+                           "r"(pack2<BF16>(v[q4 * 8 + 6], v[q4 * 8 + 7]))
+                           : "memory");
+            }
+          }
+          tc_fence_before_sync();
+          mbar_arrive(bar_acc_empty(as));
+          fence_proxy_async_smem();
+          named_bar_sync(EPI_BAR, EPI_THREADS);
+          if (epi_tid == 0) {
+            const int x0 = r0 + c * CHUNK;  // x = i + j of the chunk's first column
+            tma_store_3d(&map_band, stage, x0, r0, b);
+            tma_store_3d(&map_band, stage + S::STAGE_HALF, x0 + 64, r0, b);
+            bulk_commit();
+          }
+          ++sit;
+        } else {
+          // triangular / ragged chunk: predicated stores straight from registers.  Groups of 8 columns
+          // start on 16-byte boundaries of the band tensor (see the file header), so whole groups go out
+          // as one 16-byte store.
+          uint16_t *row = band + ((int64_t)b * p.M + i) * W;
+#pragma unroll
+          for (int g = 0; g < 4; g++) {
+            uint32_t v[32];
+            tmem_ld_x32(taddr + g * 32, v);
+            tmem_ld_wait();
+            if (i < p.M) {
+#pragma unroll
+              for (int q4 = 0; q4 < 4; q4++) {
+                const int kk0 = g * 32 + q4 * 8;
+                const int j0 = c * CHUNK + kk0 - rr;
+                if (j0 + 7 < 0 || j0 > 2 * p.w) continue;
+                if (edge) {
+#pragma unroll
+                  for (int e = 0; e < 8; e++)
+                    if (kk0 + e < kk_lo || kk0 + e >= kk_hi) v[q4 * 8 + e] = 0u;
+                }
+                if (j0 >= 0 && j0 + 7 <= 2 * p.w) {
+                  uint4 o;
+                  o.x = pack2<BF16>(v[q4 * 8 + 0], v[q4 * 8 + 1]);
+                  o.y = pack2<BF16>(v[q4 * 8 + 2], v[q4 * 8 + 3]);
+                  o.z = pack2<BF16>(v[q4 * 8 + 4], v[q4 * 8 + 5]);
+                  o.w = pack2<BF16>(v[q4 * 8 + 6], v[q4 * 8 + 7]);
+                  *reinterpret_cast<uint4 *>(row + j0) = o;
+                } else {
+#pragma unroll
+                  for (int e = 0; e < 8; e++)
+                    if (j0 + e >= 0 && j0 + e <= 2 * p.w) row[j0 + e] = pack1<BF16>(v[q4 * 8 + e]);
+                }
+              }
+            }
+          }
+          tc_fence_before_sync();
+          mbar_arrive(bar_acc_empty(as));
+        }
+      }
+    }
+    if (epi_tid == 0) bulk_wait_all();
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) atomicOr(&g_device_status, ST_NT_TIMEOUT);
+    // give copies and MMAs that may still be in flight time to land before shared and tensor memory go away
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------------
+
+using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                              const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(ptr);
+  });
+  return fn;
+}
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (!cached[dev]) {
+    int n = 0;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    cached[dev] = n > 0 ? n : 148;
+  }
+  return cached[dev];
+}
+
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+CUtensorMapSwizzle swizzle_for(int bytes) {
+  return bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
+}
+
+// 3-D map (columns, rows, batch) over a 16-bit operand with unit column stride; box = (boxk x 128 x 1).
+bool make_operand_map(CUtensorMap *m, bool bf16, const void *data, int cols, int rows, int batch, int64_t stride_r,
+                      int64_t stride_b, int boxk) {
+  const cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};
+  const cuuint64_t strides[2] = {(cuuint64_t)stride_r * 2, (cuuint64_t)(batch > 1 ? stride_b : (int64_t)rows * stride_r) * 2};
+  const cuuint32_t box[3] = {(cuuint32_t)boxk, 128, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return encode_fn()(m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                     const_cast<void *>(data), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     swizzle_for(boxk * 2), CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// The band as a pitched matrix: x = i + j in [0, M + 2w), row i with pitch 2w elements, batch with
+// pitch M*(2w+1).  Rows overlap in memory by design (pitch < extent); an in-range (x, i, b) never
+// addresses memory outside the tensor.  Box = (64 x 128 x 1), 128-byte swizzle.
+bool make_band_map(CUtensorMap *m, bool bf16, const void *band, int M, int w, int batch) {
+  const cuuint64_t dims[3] = {(cuuint64_t)M + 2ull * w, (cuuint64_t)M, (cuuint64_t)batch};
+  const cuuint64_t strides[2] = {(cuuint64_t)(2 * w) * 2, (cuuint64_t)M * (2ull * w + 1) * 2};
+  const cuuint32_t box[3] = {64, 128, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return encode_fn()(m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                     const_cast<void *>(band), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool operand_tma_ok(const void *data, int64_t sb, int64_t sr, int64_t sc, int batch) {
+  return aligned16(data) && sc == 1 && sr > 0 && (sr % 8) == 0 && (batch <= 1 || (sb > 0 && (sb % 8) == 0));
+}
+
+bool band_tma_ok(const void *band, int M, int w) { return aligned16(band) && (w % 4) == 0 && w >= 4 && (M % 8) == 0; }
+
+template <bool BF16, int NH> cudaError_t launch_nt(const Problem &p, cudaStream_t stream) {
+  using S = NtSmem<NH>;
+  using OT = KMajorTile<NH>;
+  CUtensorMap mx, my, mb;
+  if (!make_operand_map(&mx, BF16, p.a, NH, p.M, p.B, p.a_sr, p.a_sb, OT::BOXK) ||
+      !make_operand_map(&my, BF16, p.b, NH, p.Mo, p.B, p.b_sr, p.b_sb, OT::BOXK) || !make_band_map(&mb, BF16, p.o, p.M, p.w, p.B))
+    return cudaErrorInvalidValue;
+  NtParams k;
+  k.B = p.B; k.M = p.M; k.w = p.w; k.off = p.off; k.lo = p.lo; k.hi = p.hi;
+  k.tiles_per_batch = (p.M + TILE - 1) / TILE;
+  k.total_tiles = k.tiles_per_batch * p.B;
+  k.nchunks = (TILE + 2 * p.w + CHUNK - 1) / CHUNK;
+  k.band = p.o;
+  auto kern = band_nt_tc_kernel<BF16, NH>;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  // the attribute is per device; set it on every call of a new device (cheap) rather than caching per device
+  attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::ALLOC);
+  if (attr_err != cudaSuccess) return attr_err;
+  (void)once;
+  const int grid = k.total_tiles < sm_count() ? k.total_tiles : sm_count();
+  kern<<<grid, NT_THREADS, S::ALLOC, stream>>>(mx, my, mb, k);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool tensor_eligible(Primitive prim, const Problem &p) {
+  if (p.dtype != WMM_F16 && p.dtype != WMM_BF16) return false;
+  if (!encode_fn()) return false;
+  if (p.N != 32 && p.N != 64 && p.N != 128) return false;
+  if ((int64_t)p.B * ((p.M + TILE - 1) / TILE) > 0x7fffffffLL) return false;
+  switch (prim) {
+    case BAND_NT:
+      return band_tma_ok(p.o, p.M, p.w) && operand_tma_ok(p.a, p.a_sb, p.a_sr, p.a_sc, p.B) &&
+             operand_tma_ok(p.b, p.b_sb, p.b_sr, p.b_sc, p.B) && p.Mo > 0;
+    default: return false;
+  }
+}
+
+cudaError_t launch_tensor(Primitive prim, const Problem &p, cudaStream_t stream, int *launches) {
+  cudaError_t e = cudaErrorNotSupported;
+  const bool bf16 = p.dtype == WMM_BF16;
+  if (prim == BAND_NT) {
+    switch (p.N) {
+      case 32: e = bf16 ? launch_nt<true, 32>(p, stream) : launch_nt<false, 32>(p, stream); break;
+      case 64: e = bf16 ? launch_nt<true, 64>(p, stream) : launch_nt<false, 64>(p, stream); break;
+      case 128: e = bf16 ? launch_nt<true, 128>(p, stream) : launch_nt<false, 128>(p, stream); break;
+    }
+  }
+  if (e == cudaSuccess && launches) ++*launches;
+  return e;
+}
 
 }  // namespace wmm

@@ -16,8 +16,11 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 @pytest.fixture(scope="module")
 def wm():
-    import window_matmul
-    from window_matmul import _native, window_matmul as impl
+    import importlib
+
+    from window_matmul import _native
+
+    impl = importlib.import_module("window_matmul.window_matmul")  # the module, not the function of that name
 
     assert torch.cuda.is_available()
     assert os.path.exists(_native.LIB_PATH)
@@ -64,13 +67,60 @@ def test_golden_fp32_fp64_bit_exact_with_split_rounding(wm, golden):
     assert n >= 25
 
 
-def test_golden_fp32_default_fma_within_reference_tolerance(wm, golden):
+def _ref_cuda():
+    """The reference's own extension, compiled unmodified (oracle/build_ref.py), CUDA kernels included."""
+    ref_dir = os.path.join(ROOT, "oracle", "_ref")
+    if not os.path.exists(os.path.join(ref_dir, "WITH_CUDA")):
+        pytest.skip("compiled reference with CUDA kernels not present")
+    if ref_dir not in sys.path:
+        sys.path.insert(0, ref_dir)
+    import window_matmul_kernel
+
+    return window_matmul_kernel
+
+
+def test_golden_fp32_default_fma_close_to_float64_truth(wm, golden):
+    """Default fp32 mode (fused multiply-add chains, the order of the reference's CUDA kernels): fused
+    and split rounding differ at the 1e-5 level on unit-variance inputs, so the comparand here is the
+    float64 oracle, with the error an ascending fp32 chain has; the comparison with the reference's CUDA
+    kernels at rtol 1e-5 / atol 1e-6 is test_fp32_default_matches_reference_cuda_kernels."""
     for name, c in golden.items():
         if not name.endswith("float32"):
             continue
-        got = _run_all(wm, c, _w(name), torch.float32, 0)
+        w = _w(name)
+        got = _run_all(wm, c, w, torch.float32, 0)
+        d = {k: c[k] for k in ("q", "v", "att", "g_band", "g_out")}
+        d["kt"] = c["k"].transpose(0, 2, 1)
+        want = H.oracle_all(d, w, np.float64)
         for key in ("a", "gq", "gk", "o", "gatt", "gv"):
-            H.assert_fp32_close(got[key], c[key], name + "/" + key)
+            H.assert_lowp_close(got[key], want[key], name + "/" + key, rel=2e-5)
+
+
+@pytest.mark.parametrize("shape", [(2, 16, 3, 4), (2, 130, 64, 64), (2, 257, 128, 32), (4, 1024, 64, 64)])
+def test_fp32_default_matches_reference_cuda_kernels(wm, shape):
+    """Same seeded inputs through the reference's CUDA kernels (csrc/window_matmul/cuda/window_matmul_cuda.cu)
+    and through this library's default fp32 mode: rtol 1e-5 / atol 1e-6, all six results."""
+    ref = _ref_cuda()
+    B, M, Nn, w = shape
+    d = H.rand_inputs(B, M, Nn, w, seed=31)
+    q, kt, v, att, g_band, g_out = (H.to_dev(d[x], torch.float32) for x in ("q", "kt", "v", "att", "g_band", "g_out"))
+    att = att * torch.from_numpy(~H.out_of_sequence_mask(M, w)).cuda()  # the reference's kernels read those slots
+    k = kt.transpose(-1, -2)
+    torch.cuda.synchronize()  # the reference launches on the legacy default stream
+    want = {}
+    want["a"] = ref.window_matmul_forward(q, k, w)
+    want["gq"], want["gk"] = ref.window_matmul_backward(q, k, w, g_band)
+    want["o"] = ref.unwindow_matmul_forward(att, v, w)
+    want["gatt"], want["gv"] = ref.unwindow_matmul_backward(att, v, w, g_out)
+    torch.cuda.synchronize()
+    got = {}
+    got["a"] = wm.window_matmul_forward(q, k, w)
+    got["gq"], got["gk"] = wm.window_matmul_backward(q, k, w, g_band)
+    got["o"] = wm.unwindow_matmul_forward(att, v, w)
+    got["gatt"], got["gv"] = wm.unwindow_matmul_backward(att, v, w, g_out)
+    torch.cuda.synchronize()
+    for key in got:
+        H.assert_fp32_close(got[key], want[key].cpu().numpy(), key)
 
 
 def test_golden_fp16_inputs_against_fp32_oracle(wm, golden):
@@ -105,7 +155,9 @@ def test_ops_against_oracle_all_dtypes(wm, shape, dtype):
         if dtype in (torch.float16, torch.bfloat16):
             H.assert_lowp_close(got[key], want[key], key)
         elif dtype == torch.float32:
-            H.assert_fp32_close(got[key], want[key], key)
+            # fused multiply-add chains vs the oracle's separately rounded ones: see
+            # test_golden_fp32_default_fma_close_to_float64_truth
+            H.assert_lowp_close(got[key], want[key], key, rel=2e-5)
         else:
             np.testing.assert_allclose(got[key].cpu().numpy(), want[key], rtol=1e-12, atol=1e-12)
     mask = H.out_of_sequence_mask(M, w)
@@ -126,9 +178,9 @@ def test_k_in_both_memory_orders_and_grad_k_shape(wm, k_layout):
     a = wm.window_matmul_forward(q, k, w)
     gq, gk = wm.window_matmul_backward(q, k, w, g_band)
     assert gk.shape == (B, Nn, M)
-    H.assert_fp32_close(a, want["a"], "a")
-    H.assert_fp32_close(gq, want["gq"], "gq")
-    H.assert_fp32_close(gk, want["gk"], "gk")
+    H.assert_lowp_close(a, want["a"], "a", rel=2e-5)
+    H.assert_lowp_close(gq, want["gq"], "gq", rel=2e-5)
+    H.assert_lowp_close(gk, want["gk"], "gk", rel=2e-5)
 
 
 def test_unwindow_never_reads_out_of_sequence_band_slots(wm):
@@ -141,9 +193,9 @@ def test_unwindow_never_reads_out_of_sequence_band_slots(wm):
     want = H.oracle_all(d, w)
     o = wm.unwindow_matmul_forward(H.to_dev(poisoned, torch.float32), v, w)
     gatt, gv = wm.unwindow_matmul_backward(H.to_dev(poisoned, torch.float32), v, w, g_out)
-    H.assert_fp32_close(o, want["o"], "o")
-    H.assert_fp32_close(gv, want["gv"], "gv")
-    H.assert_fp32_close(gatt, want["gatt"], "gatt")
+    H.assert_lowp_close(o, want["o"], "o", rel=2e-5)
+    H.assert_lowp_close(gv, want["gv"], "gv", rel=2e-5)
+    H.assert_lowp_close(gatt, want["gatt"], "gatt", rel=2e-5)
 
 
 # ---- the reference's three-way scheme through the public, differentiable API ----------------------
@@ -320,7 +372,7 @@ def test_primitives_on_a_sequence_shard(wm, dtype):
     if dtype != torch.float32:
         d = {k: H.round_to(v, dtype) for k, v in d.items()}
     want = H.oracle_all(d, w)
-    close = H.assert_fp32_close if dtype == torch.float32 else H.assert_lowp_close
+    close = (lambda g, w_, n: H.assert_lowp_close(g, w_, n, rel=2e-5)) if dtype == torch.float32 else H.assert_lowp_close
     parts = 3
     Ml = M // parts
     gv_sum = np.zeros((B, M + 2 * w, Nn), dtype=np.float64)

@@ -1,0 +1,93 @@
+"""The tcgen05 kernels (16-bit inputs) against the fp32 oracle on the same rounded inputs.  Every call
+passes WMM_FLAG_REQUIRE_TENSOR, so a silent fall-back to the CUDA-core kernels fails the test."""
+import importlib
+
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+# (B, M, N, w): the window and hidden sizes of the benchmark configurations at reduced B and M, ragged
+# last tiles (M not a multiple of 128), windows that end inside a chunk, one-chunk windows
+SHAPES = [
+    (2, 512, 64, 64),
+    (1, 1024, 64, 256),
+    (2, 200, 64, 64),
+    (3, 136, 64, 4),
+    (1, 640, 64, 12),
+    (2, 384, 128, 128),
+    (1, 1152, 128, 512),
+    (4, 256, 32, 8),
+    (1, 768, 64, 384),
+    (2, 8, 64, 4),
+]
+
+
+@pytest.fixture(scope="module")
+def wm():
+    from window_matmul import _native
+
+    impl = importlib.import_module("window_matmul.window_matmul")
+    yield impl
+    assert _native.device_status() == 0, "a tensor-core kernel abandoned a bounded wait"
+
+
+def _inputs(shape, dtype, seed=3):
+    B, M, Nn, w = shape
+    d = H.rand_inputs(B, M, Nn, w, seed=seed, scale=1.0 / np.sqrt(Nn))
+    return {k: H.round_to(v, dtype) for k, v in d.items()}
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_band_nt_tensor(wm, shape, dtype):
+    from window_matmul import _native as N
+
+    B, M, Nn, w = shape
+    d = _inputs(shape, dtype)
+    want = H.oracle.window_matmul_forward(d["q"], np.ascontiguousarray(d["kt"].transpose(0, 2, 1)), w)
+    q, kt = H.to_dev(d["q"], dtype), H.to_dev(d["kt"], dtype)
+    band = torch.full((B, M, 2 * w + 1), float("nan"), dtype=dtype, device="cuda")  # every entry must be written
+    wm.band_nt(q, kt, w, out=band, flags=N.FLAG_REQUIRE_TENSOR)
+    torch.cuda.synchronize()
+    assert N.device_status() == 0
+    H.assert_lowp_close(band, want, "band_nt %s" % (shape,))
+    mask = H.out_of_sequence_mask(M, w)
+    assert (band.float().cpu().numpy()[:, mask] == 0).all()
+
+
+@pytest.mark.parametrize("shape", [(2, 256, 64, 64), (1, 384, 64, 256)])
+def test_band_nt_tensor_on_a_sequence_shard(wm, shape):
+    from window_matmul import _native as N
+
+    B, M, Nn, w = shape
+    dtype = torch.bfloat16
+    d = _inputs(shape, dtype)
+    want = H.oracle.window_matmul_forward(d["q"], np.ascontiguousarray(d["kt"].transpose(0, 2, 1)), w)
+    parts = 2
+    Ml = M // parts
+    for r in range(parts):
+        m0 = r * Ml
+        kt_ext = np.pad(d["kt"], ((0, 0), (w, w), (0, 0)))[:, m0:m0 + Ml + 2 * w]
+        # poison the halo rows that lie outside the global sequence: they must be masked, not multiplied
+        seq = (max(0, w - m0), min(Ml + 2 * w, M - m0 + w))
+        kt_ext = kt_ext.copy()
+        kt_ext[:, :seq[0]] = 77.0
+        kt_ext[:, seq[1]:] = 77.0
+        a = wm.band_nt(H.to_dev(d["q"][:, m0:m0 + Ml], dtype), H.to_dev(kt_ext, dtype), w, other_off=w, seq=seq,
+                       flags=N.FLAG_REQUIRE_TENSOR)
+        H.assert_lowp_close(a, want[:, m0:m0 + Ml], "shard %d" % r)
+
+
+def test_ineligible_problems_are_reported_not_faked(wm):
+    from window_matmul import _native as N
+
+    q = torch.randn(2, 64, 24, device="cuda", dtype=torch.bfloat16)  # hidden size 24: no tensor kernel
+    with pytest.raises(RuntimeError, match="UNSUPPORTED"):
+        wm.band_nt(q, q, 8, flags=N.FLAG_REQUIRE_TENSOR)
+    q = torch.randn(2, 64, 64, device="cuda", dtype=torch.float32)  # fp32 stays on the exact-order kernels
+    with pytest.raises(RuntimeError, match="UNSUPPORTED"):
+        wm.band_nt(q, q, 8, flags=N.FLAG_REQUIRE_TENSOR)
