@@ -1,0 +1,443 @@
+#!/usr/bin/env python
+"""Benchmark of the banded-contraction hot path: forward + backward of window_matmul -> unwindow_matmul.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c1|c3|c4|c5]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One "step" is one pass of the six contractions (window fwd, unwindow fwd, unwindow bwd {grad_A, grad_V},
+window bwd {grad_Q, grad_K}) over the workload.  The default workload is the configuration the headline
+metric is quoted on: B = 96 (8 batch x 12 heads), M = 4096, N = 64, w = 256, bf16, seeded N(0,1)/sqrt(N)
+inputs.  On N > 1 GPUs the batch is split evenly over the ranks (no data-path communication; strong
+scaling: the job is the same 96 sequences) and the time is the maximum over ranks.
+
+Prints ONE JSON line (rank 0).  `value` is microseconds per step with inputs resident in HBM, the six
+kernels replayed from a CUDA graph; `e2e` is the same step through the package's public, differentiable
+API with pinned HOST buffers, host->device and device->host copies inside the timed region.
+`--impl reference` times the reference's own CPU implementation (oracle/_ref, else the CPU oracle port)
+on a bounded sample of the same workload and extrapolates to the full size.
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "pytorch-window-matmul_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+WORKLOADS = {
+    # name: (B, M, N, w, dtype, distribution)
+    "c1": (4, 1024, 64, 64, "fp32", "normal"),
+    "c2": (96, 4096, 64, 256, "bf16", "normal_scaled"),
+    "c2_fp32": (96, 4096, 64, 256, "fp32", "normal_scaled"),
+    "c3": (1024, 2048, 32, 8, "fp16", "uniform"),
+    "c4": (16, 65536, 128, 512, "bf16", "normal_scaled"),
+    "c5": (64, 16384, 64, 384, "bf16", "normal"),
+}
+METRIC = "fwd+bwd window+unwindow us at B=96 M=4096 N=64 w=256"
+
+
+def algorithmic(B, M, N, w, e):
+    """Bytes and flops of one step: each distinct input read once and each output written once per
+    autograd node; 6 contractions of 2*B*M*(2w+1)*N flops."""
+    W = 2 * w + 1
+    return e * (11 * B * M * N + 5 * B * M * W), 12 * B * M * W * N
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while a timed region runs."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(0.004)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {
+            "sm_mhz": s[len(s) // 2] if s else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(s),
+        }
+
+
+def make_inputs(B, M, N, w, dist, seed, torch):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    if dist == "uniform":
+        mk = lambda: torch.rand(B, M, N, generator=g)  # noqa: E731
+    else:
+        s = (1.0 / N ** 0.5) if dist == "normal_scaled" else 1.0
+        mk = lambda: torch.randn(B, M, N, generator=g) * s  # noqa: E731
+    q, kt, v = mk(), mk(), mk()
+    go = torch.randn(B, M, N, generator=g)
+    return q, kt, v, go
+
+
+# ---------------------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the reference's CPU implementation on a bounded sample
+# ---------------------------------------------------------------------------------------------------
+
+
+def _cpu_reference_module():
+    ref_dir = os.path.join(ROOT, "oracle", "_ref")
+    if os.path.exists(os.path.join(ref_dir, "window_matmul_kernel.so")):
+        sys.path.insert(0, ref_dir)
+        try:
+            import window_matmul_kernel
+
+            return window_matmul_kernel, "reference"
+        except Exception:
+            pass
+    from oracle import oracle
+
+    return oracle, "port"
+
+
+def cpu_chain_seconds(mod, kind, q, kt, v, go, w, torch):
+    """One fwd+bwd chain on the CPU (fp32, one thread as the reference ships it).  Returns seconds."""
+    k = kt.transpose(1, 2).contiguous()
+    t0 = time.perf_counter()
+    if kind == "reference":
+        a = mod.window_matmul_forward(q, k, w)
+        mod.unwindow_matmul_forward(a, v, w)
+        ga, _gv = mod.unwindow_matmul_backward(a, v, w, go)
+        mod.window_matmul_backward(q, k, w, ga)
+    else:
+        mod.chain_fwd_bwd(q.numpy(), k.numpy(), v.numpy(), w, go.numpy())
+    return time.perf_counter() - t0
+
+
+def cpu_sample_plan(B, M, N, w, budget_s, steps):
+    """Chooses (batch entries, rows) of the per-step CPU sample so that `steps` of them fit the budget.
+    Cost model: ~1.2e-9 s per multiply-add of the six single-threaded loops (measured on this image)."""
+    per_row = 6 * (2 * w + 1) * N * 1.2e-9 * 2
+    rows_budget = max(1.0, budget_s / max(1, steps) / per_row)
+    Ms = M
+    while Ms > 4 * w and Ms > 512 and Ms > rows_budget:
+        Ms //= 2
+    Bs = int(max(1, min(B, rows_budget // Ms)))
+    return Bs, Ms
+
+
+def run_reference(args, torch):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    B, M, N, w, dt, dist = WORKLOADS[args.workload]
+    mod, kind = _cpu_reference_module()
+    torch.set_num_threads(1)
+    Bs, Ms = cpu_sample_plan(B, M, N, w, 150.0, args.steps + args.warmup)
+    q, kt, v, go = make_inputs(Bs, Ms, N, w, dist, 0, torch)
+    if dt != "fp32":  # the reference has no bf16 and accumulates fp16 in fp16: run fp32 on the rounded inputs
+        lowp = torch.bfloat16 if dt == "bf16" else torch.float16
+        q, kt, v, go = (t.to(lowp).float() for t in (q, kt, v, go))
+    for _ in range(args.warmup):
+        cpu_chain_seconds(mod, kind, q, kt, v, go, w, torch)
+    t = [cpu_chain_seconds(mod, kind, q, kt, v, go, w, torch) for _ in range(args.steps)]
+    scale = (B * M) / float(Bs * Ms)
+    step_s = sum(t) / len(t)
+    value = step_s * scale * 1e6
+    sample = "B=%d M=%d of B=%d M=%d (N=%d w=%d, fp32 on %s-rounded inputs), x%.1f extrapolated" % (Bs, Ms, B, M, N, w, dt, scale)
+    line = {
+        "impl": "reference", "metric": METRIC if args.workload == "c2" else "fwd+bwd window+unwindow us (%s)" % args.workload,
+        "value": value, "unit": "us", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": value / 1e3, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(args.workload), "reference_cpu_step_s_on_sample": step_s},
+        "cpu_baseline": {"value": value, "unit": "us", "cores": 1, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_name(key):
+    B, M, N, w, dt, dist = WORKLOADS[key]
+    return "%s: B=%d M=%d N=%d w=%d %s fwd+bwd window_matmul->unwindow_matmul, %s inputs" % (key, B, M, N, w, dt, dist)
+
+
+# ---------------------------------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------------------------------
+
+
+def run_ours(args, torch):
+    import importlib
+
+    import window_matmul as pkg
+    from window_matmul import _native as N_
+
+    impl = importlib.import_module("window_matmul.window_matmul")
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device (there is no CPU fallback); use --impl reference for the CPU arm")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist_on = world > 1
+    if dist_on:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+
+    B, M, N, w, dt, distn = WORKLOADS[args.workload]
+    dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[dt]
+    e = 2 if dt != "fp32" else 4
+    # strong scaling: the same B sequences, split evenly over the ranks (the last rank may get fewer)
+    per = (B + world - 1) // world
+    b0, b1 = min(B, rank * per), min(B, (rank + 1) * per)
+    Bl = b1 - b0
+    q, kt, v, go = make_inputs(B, M, N, w, distn, 0, torch)
+    q, kt, v, go = (t[b0:b1].to(dtype).contiguous() for t in (q, kt, v, go))
+    host = [t.pin_memory() for t in (q, kt, v, go)]
+    qd, ktd, vd, god = (t.to(dev) for t in host)
+    W = 2 * w + 1
+    a = torch.empty(Bl, M, W, dtype=dtype, device=dev)
+    ga = torch.empty_like(a)
+    o, gv, gq, gkt = (torch.empty(Bl, M, N, dtype=dtype, device=dev) for _ in range(4))
+
+    kernels = [
+        ("window_fwd band_nt", lambda: impl.band_nt(qd, ktd, w, out=a), 2 * N + W),
+        ("unwindow_fwd band_n", lambda: impl.band_n(a, vd, w, out=o), 2 * N + W),
+        ("unwindow_bwd grad_A band_nt", lambda: impl.band_nt(god, vd, w, out=ga), 2 * N + W),
+        ("unwindow_bwd grad_V band_t", lambda: impl.band_t(a, god, w, out=gv), 2 * N + W),
+        ("window_bwd grad_Q band_n", lambda: impl.band_n(ga, ktd, w, out=gq), 2 * N + W),
+        ("window_bwd grad_K band_t", lambda: impl.band_t(ga, qd, w, out=gkt), 2 * N + W),
+    ]
+
+    def step():
+        for _, fn, _ in kernels:
+            fn()
+
+    stream = torch.cuda.Stream(device=dev)
+    with torch.cuda.stream(stream):
+        for _ in range(max(3, args.warmup)):
+            step()
+        stream.synchronize()
+        graph = None
+        if Bl > 0 and not args.no_graph:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                step()
+            for _ in range(2):
+                graph.replay()
+            stream.synchronize()
+
+        def barrier():
+            torch.cuda.synchronize(dev)
+            if dist_on:
+                dist.barrier()
+            torch.cuda.synchronize(dev)
+
+        # ---- device-resident timing: K steps between two events on the launching stream ----
+        launches0 = N_.launch_count()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        with ClockSampler(local_rank) as clocks:
+            ev0.record(stream)
+            for _ in range(args.steps):
+                if graph is not None:
+                    graph.replay()
+                else:
+                    step()
+            ev1.record(stream)
+            stream.synchronize()
+        barrier()
+        elapsed_ms = ev0.elapsed_time(ev1)
+        launches = (N_.launch_count() - launches0) if graph is None else args.steps * len(kernels)
+
+        # ---- per-kernel durations (for the roofline of the dominant kernel) ----
+        per_kernel = {}
+        reps = 10
+        for name, fn, cols in kernels:
+            if Bl == 0:
+                continue
+            fn()
+            k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            stream.synchronize()
+            k0.record(stream)
+            for _ in range(reps):
+                fn()
+            k1.record(stream)
+            stream.synchronize()
+            us = k0.elapsed_time(k1) * 1e3 / reps
+            nbytes = e * Bl * M * cols
+            per_kernel[name] = {"us": round(us, 2), "alg_MB": round(nbytes / 1e6, 1), "GBps": round(nbytes / us / 1e3, 1)}
+
+        # ---- end to end through the public API, host buffers, copies inside the timed region ----
+        e2e_steps = max(3, min(args.steps, 20))
+        outs_host = [torch.empty(Bl, M, N, dtype=dtype).pin_memory() for _ in range(4)]
+
+        def e2e_step():
+            qh, kth, vh, goh = (t.to(dev, non_blocking=True) for t in host)
+            qh.requires_grad_(True)
+            kth.requires_grad_(True)
+            vh.requires_grad_(True)
+            att = pkg.window_matmul(qh, kth.transpose(-1, -2), w)
+            out = pkg.unwindow_matmul(att, vh, w)
+            out.backward(goh)
+            for dst, src in zip(outs_host, (out.detach(), qh.grad, kth.grad, vh.grad)):
+                dst.copy_(src, non_blocking=True)
+
+        if Bl > 0:
+            for _ in range(2):
+                e2e_step()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        if Bl > 0:
+            for _ in range(e2e_steps):
+                e2e_step()
+        e1.record(stream)
+        stream.synchronize()
+        barrier()
+        e2e_ms = e0.elapsed_time(e1) / e2e_steps
+
+    status = N_.device_status()
+    if status != 0:
+        raise SystemExit("bench.py: a kernel abandoned a bounded wait (device status %d); numbers are void" % status)
+
+    # max over ranks, on the device clock
+    t = torch.tensor([elapsed_ms, e2e_ms], dtype=torch.float64, device=dev)
+    if dist_on:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    elapsed_ms, e2e_ms = float(t[0]), float(t[1])
+    us_per_step = elapsed_ms * 1e3 / args.steps
+
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        total_bytes, total_flops = algorithmic(B, M, N, w, e)
+        dom = max(per_kernel.items(), key=lambda kv: kv[1]["us"]) if per_kernel else (None, None)
+        traffic = None
+        tpath = os.path.join(ROOT, "profiles", "ncu_traffic.json")
+        if dom[0] and os.path.exists(tpath):
+            with open(tpath) as f:
+                rec = json.load(f).get(args.workload, {}).get(dom[0].split()[-1])
+            if rec:  # bytes per band row, scaled to this rank's launch (traffic grows in proportion to rows)
+                traffic = rec["dram_bytes_per_row"] * Bl * M
+        line = {
+            "metric": METRIC if args.workload == "c2" else "fwd+bwd window+unwindow us (%s)" % args.workload,
+            "value": us_per_step, "unit": "us", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+            "ms_per_step": us_per_step / 1e3, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+            "dtype": dt.replace("fp", "f"), "data": "synthetic",
+            "config": {
+                "workload": workload_name(args.workload), "batch_per_gpu": per,
+                "l2": "no flush: one step touches %.0f MB per GPU, larger than the 126 MB L2" % (total_bytes / world / 1e6),
+                "launch": "cuda graph of 6 kernels" if graph is not None else "6 stream launches",
+                "k_layout": "transposed view of (B,M,N)",
+            },
+            "step_roofline": {
+                "alg_MB": round(total_bytes / 1e6, 1), "alg_GFLOP": round(total_flops / 1e9, 1),
+                "achieved_GBps": round(total_bytes / world / (us_per_step * 1e-6) / 1e9, 1) * world,
+                "frac_of_%s_hbm" % peak_kind: round(total_bytes / world / (us_per_step * 1e-6) / 1e9 / peak, 4),
+                "TFLOPs": round(total_flops / (us_per_step * 1e-6) / 1e12, 1),
+            },
+            "roofline": {
+                "bound": "hbm", "kernel": dom[0], "achieved": dom[1]["GBps"] if dom[0] else None, "peak": peak,
+                "unit": "GB/s", "frac": round(dom[1]["GBps"] / peak, 4) if dom[0] else None, "peak_kind": peak_kind,
+                "traffic": traffic,
+            },
+            "per_kernel": per_kernel,
+            "e2e": {
+                "value": e2e_ms * 1e3, "unit": "us", "h2d_bytes_per_step": 4 * Bl * M * N * e * world,
+                "d2h_bytes_per_step": 4 * Bl * M * N * e * world, "steps": e2e_steps,
+            },
+            "gpu_launches": int(launches),
+            "clocks": clocks.summary(),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            mod, kind = _cpu_reference_module()
+            torch.set_num_threads(1)
+            Bs, Ms = cpu_sample_plan(B, M, N, w, 15.0, 2)
+            cq, ckt, cv, cgo = make_inputs(Bs, Ms, N, w, distn, 0, torch)
+            if dt != "fp32":
+                cq, ckt, cv, cgo = (x.to(dtype).float() for x in (cq, ckt, cv, cgo))
+            cpu_chain_seconds(mod, kind, cq, ckt, cv, cgo, w, torch)  # the first call carries one-off warm-up
+            secs = cpu_chain_seconds(mod, kind, cq, ckt, cv, cgo, w, torch)
+            scale = (B * M) / float(Bs * Ms)
+            line["cpu_baseline"] = {
+                "value": secs * scale * 1e6, "unit": "us", "cores": 1, "kind": kind,
+                "sample": "B=%d M=%d of B=%d M=%d, fp32 on %s-rounded inputs, %.2f s measured, x%.1f extrapolated; host has %d cores, "
+                          "the reference's loops use one" % (Bs, Ms, B, M, dt, secs, scale, os.cpu_count()),
+            }
+        print(json.dumps(line), flush=True)
+    if dist_on:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-graph", action="store_true", help="launch the six kernels on the stream instead of a CUDA graph")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    import torch
+
+    if args.impl == "reference":
+        run_reference(args, torch)
+    else:
+        run_ours(args, torch)
+
+
+if __name__ == "__main__":
+    main()

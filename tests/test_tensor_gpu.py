@@ -59,6 +59,69 @@ def test_band_nt_tensor(wm, shape, dtype):
     assert (band.float().cpu().numpy()[:, mask] == 0).all()
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_band_n_tensor(wm, shape, dtype):
+    from window_matmul import _native as N
+
+    B, M, Nn, w = shape
+    d = _inputs(shape, dtype)
+    want = H.oracle.unwindow_matmul_forward(d["att"], d["v"], w)
+    # out-of-sequence band slots hold NaN: they must never reach the product
+    att = d["att"].copy()
+    att[:, H.out_of_sequence_mask(M, w)] = np.nan
+    out = torch.full((B, M, Nn), float("nan"), dtype=dtype, device="cuda")
+    wm.band_n(H.to_dev(att, dtype), H.to_dev(d["v"], dtype), w, out=out, flags=N.FLAG_REQUIRE_TENSOR)
+    torch.cuda.synchronize()
+    assert N.device_status() == 0
+    H.assert_lowp_close(out, want, "band_n %s" % (shape,))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [s for s in SHAPES if s[3] % 8 == 0])
+def test_band_t_tensor(wm, shape, dtype):
+    from window_matmul import _native as N
+
+    B, M, Nn, w = shape
+    d = _inputs(shape, dtype)
+    _, want = H.oracle.unwindow_matmul_backward(d["att"], d["v"], w, d["g_out"])
+    att = d["att"].copy()
+    att[:, H.out_of_sequence_mask(M, w)] = np.nan
+    out = torch.full((B, M, Nn), float("nan"), dtype=dtype, device="cuda")
+    wm.band_t(H.to_dev(att, dtype), H.to_dev(d["g_out"], dtype), w, out=out, flags=N.FLAG_REQUIRE_TENSOR)
+    torch.cuda.synchronize()
+    assert N.device_status() == 0
+    H.assert_lowp_close(out, want, "band_t %s" % (shape,))
+
+
+@pytest.mark.parametrize("shape", [(2, 256, 64, 64), (1, 384, 64, 256)])
+def test_band_n_and_band_t_tensor_on_a_sequence_shard(wm, shape):
+    from window_matmul import _native as N
+
+    B, M, Nn, w = shape
+    dtype = torch.bfloat16
+    d = _inputs(shape, dtype)
+    want_o = H.oracle.unwindow_matmul_forward(d["att"], d["v"], w)
+    _, want_gv = H.oracle.unwindow_matmul_backward(d["att"], d["v"], w, d["g_out"])
+    parts = 2
+    Ml = M // parts
+    gv = np.zeros((B, M + 2 * w, Nn))
+    for r in range(parts):
+        m0 = r * Ml
+        seq = (max(0, w - m0), min(Ml + 2 * w, M - m0 + w))
+        v_ext = np.pad(d["v"], ((0, 0), (w, w), (0, 0)))[:, m0:m0 + Ml + 2 * w].copy()
+        v_ext[:, :seq[0]] = np.nan
+        v_ext[:, seq[1]:] = np.nan
+        att = H.to_dev(d["att"][:, m0:m0 + Ml], dtype)
+        o = wm.band_n(att, H.to_dev(v_ext, dtype), w, other_off=w, seq=seq, flags=N.FLAG_REQUIRE_TENSOR)
+        H.assert_lowp_close(o, want_o[:, m0:m0 + Ml], "o shard %d" % r)
+        part = wm.band_t(att, H.to_dev(d["g_out"][:, m0:m0 + Ml], dtype), w, other_rows=Ml + 2 * w, other_off=w, seq=seq,
+                         flags=N.FLAG_REQUIRE_TENSOR)
+        assert (part[:, :seq[0]] == 0).all() and (part[:, seq[1]:] == 0).all()
+        gv[:, m0:m0 + Ml + 2 * w] += part.double().cpu().numpy()
+    H.assert_lowp_close(torch.from_numpy(gv[:, w:w + M]), want_gv, "gv summed over shards")
+
+
 @pytest.mark.parametrize("shape", [(2, 256, 64, 64), (1, 384, 64, 256)])
 def test_band_nt_tensor_on_a_sequence_shard(wm, shape):
     from window_matmul import _native as N
