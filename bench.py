@@ -311,9 +311,19 @@ def run_ours(args, torch):
             fn()
             k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             stream.synchronize()
+            kgraph = None
+            if not args.no_graph:  # replayed from a graph so that host launch overhead cannot hide in the number
+                kgraph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(kgraph, stream=stream):
+                    for _ in range(reps):
+                        fn()
+                stream.synchronize()
             k0.record(stream)
-            for _ in range(reps):
-                fn()
+            if kgraph is not None:
+                kgraph.replay()
+            else:
+                for _ in range(reps):
+                    fn()
             k1.record(stream)
             stream.synchronize()
             us = k0.elapsed_time(k1) * 1e3 / reps
@@ -335,13 +345,14 @@ def run_ours(args, torch):
             for dst, src in zip(outs_host, (out.detach(), qh.grad, kth.grad, vh.grad)):
                 dst.copy_(src, non_blocking=True)
 
-        if Bl > 0:
+        run_e2e = Bl > 0 and not args.skip_e2e
+        if run_e2e:
             for _ in range(2):
                 e2e_step()
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
-        if Bl > 0:
+        if run_e2e:
             for _ in range(e2e_steps):
                 e2e_step()
         e1.record(stream)
@@ -372,7 +383,7 @@ def run_ours(args, torch):
             if rec:  # bytes per band row, scaled to this rank's launch (traffic grows in proportion to rows)
                 traffic = rec["dram_bytes_per_row"] * Bl * M
         line = {
-            "metric": METRIC if args.workload == "c2" else "fwd+bwd window+unwindow us (%s)" % args.workload,
+            "metric": METRIC if args.workload == "c2" and not args.batch else "fwd+bwd window+unwindow us (%s)" % args.workload,
             "value": us_per_step, "unit": "us", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
             "ms_per_step": us_per_step / 1e3, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
             "dtype": dt.replace("fp", "f"), "data": "synthetic",
@@ -430,9 +441,14 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-graph", action="store_true", help="launch the six kernels on the stream instead of a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=0, help="override B of the workload (small cases for profiling)")
+    ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     args = ap.parse_args()
     import torch
 
+    if args.batch > 0:
+        B, M, N, w, dt, dist = WORKLOADS[args.workload]
+        WORKLOADS[args.workload] = (args.batch, M, N, w, dt, dist)
     if args.impl == "reference":
         run_reference(args, torch)
     else:

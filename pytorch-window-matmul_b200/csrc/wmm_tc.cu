@@ -39,12 +39,7 @@ using namespace ptx;
 constexpr int TILE = 128;       // band rows per tile = MMA M
 constexpr int CHUNK = 128;      // positions per chunk = MMA N of band_nt
 constexpr int ACC_STAGES = 4;   // 4 x 128 TMEM columns
-constexpr int NT_THREADS = 192;
-constexpr int EPI_THREADS = 128;
-constexpr uint32_t EPI_BAR = 1;
-
-// Status codes OR-ed into g_device_status when a bounded wait runs out.
-constexpr unsigned long long ST_NT_TIMEOUT = 1ull << 0;
+// Status codes OR-ed into g_device_status when a bounded wait runs out: bit 0 band_nt, bit 1 band_n / band_t.
 
 // A (128 rows x NH) 16-bit operand tile in shared memory, K-major, written by TMA with the hardware
 // swizzle and read by tcgen05.mma through a matching descriptor.  Rows are SW_BYTES long; wider tiles
@@ -84,245 +79,7 @@ template <bool BF16> __device__ __forceinline__ uint16_t pack1(uint32_t bits) {
   }
 }
 
-struct NtParams {
-  int B, M, w, off, lo, hi;
-  int tiles_per_batch, total_tiles, nchunks;
-  void *band;
-};
-
-template <int NH> struct NtSmem {
-  using OT = KMajorTile<NH>;
-  static constexpr int QS = 2;
-  static constexpr int KS = NH >= 128 ? 2 : 4;
-  static constexpr int STAGE_HALF = TILE * 128;  // 128 rows x 64 columns x 2 bytes
-  static constexpr int OFF_Q = 0;
-  static constexpr int OFF_K = OFF_Q + QS * OT::BYTES;
-  static constexpr int OFF_STAGE = OFF_K + KS * OT::BYTES;
-  static constexpr int OFF_BARS = OFF_STAGE + 2 * 2 * STAGE_HALF;
-  static constexpr int NBARS = 2 * QS + 2 * KS + 2 * ACC_STAGES;
-  static constexpr int OFF_MISC = OFF_BARS + NBARS * 8;
-  static constexpr int BYTES = OFF_MISC + 32;
-  static constexpr int ALLOC = BYTES + 1024;  // slack to align the base to 1024 B
-};
-
-// band_nt: Band = band(X Y^T).  One MMA chunk = X tile (128 x NH) times 128 rows of Y.
-template <bool BF16, int NH>
-__global__ void __launch_bounds__(NT_THREADS, 1)
-band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
-                  const __grid_constant__ CUtensorMap map_band, const NtParams p) {
-  using S = NtSmem<NH>;
-  using OT = KMajorTile<NH>;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t *base_ptr = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t bars = base + S::OFF_BARS;
-  auto bar_q_full = [&](int s) { return bars + 8u * s; };
-  auto bar_q_empty = [&](int s) { return bars + 8u * (S::QS + s); };
-  auto bar_k_full = [&](int s) { return bars + 8u * (2 * S::QS + s); };
-  auto bar_k_empty = [&](int s) { return bars + 8u * (2 * S::QS + S::KS + s); };
-  auto bar_acc_full = [&](int s) { return bars + 8u * (2 * S::QS + 2 * S::KS + s); };
-  auto bar_acc_empty = [&](int s) { return bars + 8u * (2 * S::QS + 2 * S::KS + ACC_STAGES + s); };
-  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + S::OFF_MISC);
-  volatile int *abort_flag = reinterpret_cast<volatile int *>(base_ptr + S::OFF_MISC + 4);
-  volatile int *epi_ok = reinterpret_cast<volatile int *>(base_ptr + S::OFF_MISC + 8);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < S::QS; s++) { mbar_init(bar_q_full(s), 1); mbar_init(bar_q_empty(s), 1); }
-    for (int s = 0; s < S::KS; s++) { mbar_init(bar_k_full(s), 1); mbar_init(bar_k_empty(s), 1); }
-    for (int s = 0; s < ACC_STAGES; s++) { mbar_init(bar_acc_full(s), 1); mbar_init(bar_acc_empty(s), EPI_THREADS); }
-    *abort_flag = 0;
-    *epi_ok = 1;
-    fence_mbar_init();
-    prefetch_tmap(&map_x);
-    prefetch_tmap(&map_y);
-    prefetch_tmap(&map_band);
-  }
-  if (warp == 1) {
-    tmem_alloc(base + S::OFF_MISC, 512);
-    tmem_relinquish();
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem_base = *tmem_slot;
-
-  if (warp == 0) {
-    // ---------------- TMA producer ----------------
-    if (lane == 0) {
-      int qit = 0, kit = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x, ++qit) {
-        const int b = tile / p.tiles_per_batch, r0 = (tile % p.tiles_per_batch) * TILE;
-        const int qs = qit % S::QS;
-        if (!(ok = mbar_wait(bar_q_empty(qs), ((qit / S::QS) & 1) ^ 1, abort_flag))) break;
-        mbar_expect_tx(bar_q_full(qs), OT::BYTES);
-#pragma unroll
-        for (int bx = 0; bx < OT::NBOX; bx++)
-          tma_load_3d(base + S::OFF_Q + qs * OT::BYTES + bx * OT::BOX_BYTES, &map_x, bar_q_full(qs), bx * OT::BOXK, r0, b);
-        for (int c = 0; c < p.nchunks; ++c, ++kit) {
-          const int ks = kit % S::KS;
-          if (!(ok = mbar_wait(bar_k_empty(ks), ((kit / S::KS) & 1) ^ 1, abort_flag))) break;
-          mbar_expect_tx(bar_k_full(ks), OT::BYTES);
-          const int p0 = r0 - p.w + p.off + c * CHUNK;
-#pragma unroll
-          for (int bx = 0; bx < OT::NBOX; bx++)
-            tma_load_3d(base + S::OFF_K + ks * OT::BYTES + bx * OT::BOX_BYTES, &map_y, bar_k_full(ks), bx * OT::BOXK, p0, b);
-        }
-      }
-    }
-  } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      constexpr uint32_t IDESC = instr_desc_f16(BF16, false, false, TILE, CHUNK);
-      int qit = 0, kit = 0, ait = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x, ++qit) {
-        const int qs = qit % S::QS;
-        if (!(ok = mbar_wait(bar_q_full(qs), (qit / S::QS) & 1, abort_flag))) break;
-        const uint32_t q_addr = base + S::OFF_Q + qs * OT::BYTES;
-        for (int c = 0; c < p.nchunks; ++c, ++kit, ++ait) {
-          const int ks = kit % S::KS, as = ait % ACC_STAGES;
-          if (!(ok = mbar_wait(bar_k_full(ks), (kit / S::KS) & 1, abort_flag))) break;
-          if (!(ok = mbar_wait(bar_acc_empty(as), ((ait / ACC_STAGES) & 1) ^ 1, abort_flag))) break;
-          tc_fence_after_sync();
-          const uint32_t k_addr = base + S::OFF_K + ks * OT::BYTES;
-#pragma unroll
-          for (int s = 0; s < OT::KSTEPS; s++)
-            umma_f16(tmem_base + as * CHUNK, smem_desc(OT::DESC, q_addr + OT::kstep_offset(s)),
-                     smem_desc(OT::DESC, k_addr + OT::kstep_offset(s)), IDESC, s > 0 ? 1u : 0u);
-          umma_commit(bar_k_empty(ks));
-          umma_commit(bar_acc_full(as));
-        }
-        if (ok) umma_commit(bar_q_empty(qs));
-      }
-    }
-  } else {
-    // ---------------- epilogue: 128 threads, thread <-> band row of the tile ----------------
-    const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 belong to this warp
-    const int rr = quarter * 32 + lane;
-    const int epi_tid = threadIdx.x - 64;
-    const int W = 2 * p.w + 1;
-    uint16_t *band = static_cast<uint16_t *>(p.band);
-    int ait = 0, sit = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
-      const int b = tile / p.tiles_per_batch, r0 = (tile % p.tiles_per_batch) * TILE;
-      const int i = r0 + rr;
-      for (int c = 0; c < p.nchunks; ++c, ++ait) {
-        const int as = ait % ACC_STAGES;
-        const bool full = (c >= 1) && (c * CHUNK + CHUNK - 1 <= 2 * p.w);
-        const int sb = sit & 1;
-        if (epi_tid == 0) {
-          int good = mbar_wait(bar_acc_full(as), (ait / ACC_STAGES) & 1, abort_flag) ? 1 : 0;
-          if (full) bulk_wait_read<1>();  // the store that last read staging buffer `sb` has drained
-          *epi_ok = good;
-        }
-        named_bar_sync(EPI_BAR, EPI_THREADS);
-        if (!(ok = (*epi_ok != 0))) break;
-        tc_fence_after_sync();
-        const uint32_t taddr = tmem_base + as * CHUNK + ((uint32_t)(quarter * 32) << 16);
-        // positions of this chunk that lie inside the sequence: kk in [kk_lo, kk_hi)
-        const int p0 = r0 - p.w + p.off + c * CHUNK;
-        const int kk_lo = p.lo - p0, kk_hi = p.hi - p0;
-        const bool edge = kk_lo > 0 || kk_hi < CHUNK;
-        if (full) {
-          const uint32_t stage = base + S::OFF_STAGE + sb * 2 * S::STAGE_HALF;
-#pragma unroll
-          for (int g = 0; g < 4; g++) {
-            uint32_t v[32];
-            tmem_ld_x32(taddr + g * 32, v);
-            tmem_ld_wait();
-            if (edge) {
-#pragma unroll
-              for (int e = 0; e < 32; e++) {
-                const int kk = g * 32 + e;
-                if (kk < kk_lo || kk >= kk_hi) v[e] = 0u;
-              }
-            }
-            const uint32_t half_base = stage + (g >> 1) * S::STAGE_HALF + rr * 128;
-#pragma unroll
-            for (int q4 = 0; q4 < 4; q4++) {
-              const int cc = (g & 1) * 4 + q4;  // 16-byte column of the 128-byte staging row
-              const uint32_t a = half_base + ((cc ^ (rr & 7)) << 4);
-              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(pack2<BF16>(v[q4 * 8 + 0], v[q4 * 8 + 1])),
-                           "r"(pack2<BF16>(v[q4 * 8 + 2], v[q4 * 8 + 3])), "r"(pack2<BF16>(v[q4 * 8 + 4], v[q4 * 8 + 5])),
-                           "r"(pack2<BF16>(v[q4 * 8 + 6], v[q4 * 8 + 7]))
-                           : "memory");
-            }
-          }
-          tc_fence_before_sync();
-          mbar_arrive(bar_acc_empty(as));
-          fence_proxy_async_smem();
-          named_bar_sync(EPI_BAR, EPI_THREADS);
-          if (epi_tid == 0) {
-            const int x0 = r0 + c * CHUNK;  // x = i + j of the chunk's first column
-            tma_store_3d(&map_band, stage, x0, r0, b);
-            tma_store_3d(&map_band, stage + S::STAGE_HALF, x0 + 64, r0, b);
-            bulk_commit();
-          }
-          ++sit;
-        } else {
-          // triangular / ragged chunk: predicated stores straight from registers.  Groups of 8 columns
-          // start on 16-byte boundaries of the band tensor (see the file header), so whole groups go out
-          // as one 16-byte store.
-          uint16_t *row = band + ((int64_t)b * p.M + i) * W;
-#pragma unroll
-          for (int g = 0; g < 4; g++) {
-            uint32_t v[32];
-            tmem_ld_x32(taddr + g * 32, v);
-            tmem_ld_wait();
-            if (i < p.M) {
-#pragma unroll
-              for (int q4 = 0; q4 < 4; q4++) {
-                const int kk0 = g * 32 + q4 * 8;
-                const int j0 = c * CHUNK + kk0 - rr;
-                if (j0 + 7 < 0 || j0 > 2 * p.w) continue;
-                if (edge) {
-#pragma unroll
-                  for (int e = 0; e < 8; e++)
-                    if (kk0 + e < kk_lo || kk0 + e >= kk_hi) v[q4 * 8 + e] = 0u;
-                }
-                if (j0 >= 0 && j0 + 7 <= 2 * p.w) {
-                  uint4 o;
-                  o.x = pack2<BF16>(v[q4 * 8 + 0], v[q4 * 8 + 1]);
-                  o.y = pack2<BF16>(v[q4 * 8 + 2], v[q4 * 8 + 3]);
-                  o.z = pack2<BF16>(v[q4 * 8 + 4], v[q4 * 8 + 5]);
-                  o.w = pack2<BF16>(v[q4 * 8 + 6], v[q4 * 8 + 7]);
-                  *reinterpret_cast<uint4 *>(row + j0) = o;
-                } else {
-#pragma unroll
-                  for (int e = 0; e < 8; e++)
-                    if (j0 + e >= 0 && j0 + e <= 2 * p.w) row[j0 + e] = pack1<BF16>(v[q4 * 8 + e]);
-                }
-              }
-            }
-          }
-          tc_fence_before_sync();
-          mbar_arrive(bar_acc_empty(as));
-        }
-      }
-    }
-    if (epi_tid == 0) bulk_wait_all();
-  }
-
-  // ---------------- teardown ----------------
-  tc_fence_before_sync();
-  __syncthreads();
-  if (*abort_flag) {
-    if (threadIdx.x == 0) atomicOr(&g_device_status, ST_NT_TIMEOUT);
-    // give copies and MMAs that may still be in flight time to land before shared and tensor memory go away
-    const uint64_t t0 = globaltimer_ns();
-    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
-    __syncthreads();
-  }
-  if (warp == 1) {
-    tc_fence_after_sync();
-    tmem_dealloc(tmem_base, 512);
-  }
-}
-
+#include "wmm_tc_nt.cuh"
 
 // ---------------------------------------------------------------------------------------------------
 // band_n (TRANSPOSED = false):  Out[i, :] = sum_p Band[i, p] Y[p, :]      tile = 128 band rows i
@@ -337,7 +94,7 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
 // ---------------------------------------------------------------------------------------------------
 
 constexpr int MM_THREADS = 320;  // producer, MMA, 4 mask warps, 4 epilogue warps
-constexpr uint32_t MM_EPI_BAR = 2;
+constexpr uint32_t MM_EPI_BAR = 3;
 constexpr unsigned long long ST_MM_TIMEOUT = 1ull << 1;
 
 struct MmParams {
@@ -686,6 +443,7 @@ template <bool BF16, int NH> cudaError_t launch_nt(const Problem &p, cudaStream_
   k.tiles_per_batch = (p.M + TILE - 1) / TILE;
   k.total_tiles = k.tiles_per_batch * p.B;
   k.nchunks = (TILE + 2 * p.w + CHUNK - 1) / CHUNK;
+  k.paired = (p.w % 64 == 0) ? 1 : 0;
   k.band = p.o;
   auto kern = band_nt_tc_kernel<BF16, NH>;
   // the attribute is per device; setting it on every call is cheap and needs no per-device cache

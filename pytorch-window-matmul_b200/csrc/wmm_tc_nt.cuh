@@ -1,0 +1,341 @@
+// band_nt on tensor cores: Band = band(X Y^T).  Included by wmm_tc.cu (inside namespace wmm::<anon>).
+//
+// One MMA chunk = X tile (128 rows x NH) times 128 rows of Y -> a 128 x 128 fp32 accumulator in TMEM.
+// A tile of 128 band rows needs ceil((128 + 2w) / 128) chunks.  The epilogue turns accumulators into
+// band storage:
+//   * a chunk that lies wholly inside the band is converted, written to a swizzled staging buffer and
+//     stored with two TMA box stores through the pitched view of the band (see wmm_tc.cu);
+//   * the first and last chunk of a tile are triangular.  When 2w is a multiple of 128 the two triangles
+//     are complementary: in the pitched view (pitch 2w) the last chunk of row i occupies the same line
+//     as the first chunk of row i+1, so first-chunk row r goes to staging line r (columns >= r), last-
+//     chunk row r to line r+1 (columns <= r), and the merged 128 x 128 box is stored by TMA like a full
+//     chunk.  Only the last valid row's last-chunk piece (one row, <= 256 bytes) is written directly.
+//   * for other windows the triangular chunks are written with predicated 16-byte stores from registers.
+//
+// Warps: 0 = TMA producer, 1 = MMA issuer / TMEM owner, 2-5 and 6-9 = two epilogue groups that take
+// work items (a full chunk, or the merged first+last pair) alternately, each with its own staging
+// buffer, so conversion of one item overlaps the drain of the other.
+
+constexpr int NT_THREADS = 320;
+constexpr int EPI_THREADS = 128;
+constexpr unsigned long long ST_NT_TIMEOUT = 1ull << 0;
+
+struct NtParams {
+  int B, M, w, off, lo, hi;
+  int tiles_per_batch, total_tiles, nchunks;
+  int paired;  // 2w is a multiple of 128: merge first and last chunk of a tile
+  void *band;
+};
+
+template <int NH> struct NtSmem {
+  using OT = KMajorTile<NH>;
+  static constexpr int QS = 2;
+  static constexpr int KS = NH >= 128 ? 2 : 4;
+  static constexpr int STAGE_HALF = TILE * 128;  // 128 lines x 64 columns x 2 bytes
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = OFF_Q + QS * OT::BYTES;
+  static constexpr int OFF_STAGE = OFF_K + KS * OT::BYTES;  // one 32 KB buffer per epilogue group
+  static constexpr int OFF_BARS = OFF_STAGE + 2 * 2 * STAGE_HALF;
+  static constexpr int NBARS = 2 * QS + 2 * KS + 2 * ACC_STAGES;
+  static constexpr int OFF_MISC = OFF_BARS + NBARS * 8;
+  static constexpr int BYTES = OFF_MISC + 32;
+  static constexpr int ALLOC = BYTES + 1024;  // slack to align the base to 1024 B
+};
+
+// 8 packed 16-bit values (one 16-byte piece) from 8 fp32 accumulator bit patterns
+template <bool BF16> __device__ __forceinline__ uint4 pack8(const uint32_t *v) {
+  uint4 o;
+  o.x = pack2<BF16>(v[0], v[1]);
+  o.y = pack2<BF16>(v[2], v[3]);
+  o.z = pack2<BF16>(v[4], v[5]);
+  o.w = pack2<BF16>(v[6], v[7]);
+  return o;
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, const uint4 &o) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o.x), "r"(o.y), "r"(o.z), "r"(o.w) : "memory");
+}
+__device__ __forceinline__ void st_shared_u16(uint32_t addr, uint16_t v) {
+  asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"(v) : "memory");
+}
+// address of the 16-byte piece (line, column group cg = column / 8) of a 128 x 128 staging box
+__device__ __forceinline__ uint32_t stage_addr(uint32_t stage, int line, int cg) {
+  return stage + (cg >> 3) * (TILE * 128) + line * 128 + (((cg & 7) ^ (line & 7)) << 4);
+}
+// zero the accumulator values of 32 columns starting at column kbase whose position is outside [kk_lo, kk_hi)
+__device__ __forceinline__ void mask_columns(uint32_t (&v)[32], int kbase, int kk_lo, int kk_hi) {
+#pragma unroll
+  for (int e = 0; e < 32; e++)
+    if (kbase + e < kk_lo || kbase + e >= kk_hi) v[e] = 0u;
+}
+
+template <bool BF16, int NH>
+__global__ void __launch_bounds__(NT_THREADS, 1)
+band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
+                  const __grid_constant__ CUtensorMap map_band, const NtParams p) {
+  using S = NtSmem<NH>;
+  using OT = KMajorTile<NH>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t *base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bars = base + S::OFF_BARS;
+  auto bar_q_full = [&](int s) { return bars + 8u * s; };
+  auto bar_q_empty = [&](int s) { return bars + 8u * (S::QS + s); };
+  auto bar_k_full = [&](int s) { return bars + 8u * (2 * S::QS + s); };
+  auto bar_k_empty = [&](int s) { return bars + 8u * (2 * S::QS + S::KS + s); };
+  auto bar_acc_full = [&](int s) { return bars + 8u * (2 * S::QS + 2 * S::KS + s); };
+  auto bar_acc_empty = [&](int s) { return bars + 8u * (2 * S::QS + 2 * S::KS + ACC_STAGES + s); };
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + S::OFF_MISC);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(base_ptr + S::OFF_MISC + 4);
+  volatile int *epi_ok = reinterpret_cast<volatile int *>(base_ptr + S::OFF_MISC + 8);  // [2], one per group
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool paired = p.paired != 0;
+  // order in which the chunks of a tile are loaded and multiplied: with pairing the last chunk comes
+  // second, so that both triangles are in TMEM together
+  auto chunk_at = [&](int k) -> int { return !paired ? k : (k == 0 ? 0 : (k == 1 ? p.nchunks - 1 : k - 1)); };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S::QS; s++) { mbar_init(bar_q_full(s), 1); mbar_init(bar_q_empty(s), 1); }
+    for (int s = 0; s < S::KS; s++) { mbar_init(bar_k_full(s), 1); mbar_init(bar_k_empty(s), 1); }
+    for (int s = 0; s < ACC_STAGES; s++) { mbar_init(bar_acc_full(s), 1); mbar_init(bar_acc_empty(s), EPI_THREADS); }
+    *abort_flag = 0;
+    epi_ok[0] = 1;
+    epi_ok[1] = 1;
+    fence_mbar_init();
+    prefetch_tmap(&map_x);
+    prefetch_tmap(&map_y);
+    prefetch_tmap(&map_band);
+  }
+  if (warp == 1) {
+    tmem_alloc(base + S::OFF_MISC, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int qit = 0, kit = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x, ++qit) {
+        const int b = tile / p.tiles_per_batch, r0 = (tile % p.tiles_per_batch) * TILE;
+        const int qs = qit % S::QS;
+        if (!(ok = mbar_wait(bar_q_empty(qs), ((qit / S::QS) & 1) ^ 1, abort_flag))) break;
+        mbar_expect_tx(bar_q_full(qs), OT::BYTES);
+#pragma unroll
+        for (int bx = 0; bx < OT::NBOX; bx++)
+          tma_load_3d(base + S::OFF_Q + qs * OT::BYTES + bx * OT::BOX_BYTES, &map_x, bar_q_full(qs), bx * OT::BOXK, r0, b);
+        for (int k = 0; k < p.nchunks; ++k, ++kit) {
+          const int ks = kit % S::KS;
+          if (!(ok = mbar_wait(bar_k_empty(ks), ((kit / S::KS) & 1) ^ 1, abort_flag))) break;
+          mbar_expect_tx(bar_k_full(ks), OT::BYTES);
+          const int p0 = r0 - p.w + p.off + chunk_at(k) * CHUNK;
+#pragma unroll
+          for (int bx = 0; bx < OT::NBOX; bx++)
+            tma_load_3d(base + S::OFF_K + ks * OT::BYTES + bx * OT::BOX_BYTES, &map_y, bar_k_full(ks), bx * OT::BOXK, p0, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t IDESC = instr_desc_f16(BF16, false, false, TILE, CHUNK);
+      int qit = 0, kit = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x, ++qit) {
+        const int qs = qit % S::QS;
+        if (!(ok = mbar_wait(bar_q_full(qs), (qit / S::QS) & 1, abort_flag))) break;
+        const uint32_t q_addr = base + S::OFF_Q + qs * OT::BYTES;
+        for (int k = 0; k < p.nchunks; ++k, ++kit) {
+          const int ks = kit % S::KS, as = kit % ACC_STAGES;
+          if (!(ok = mbar_wait(bar_k_full(ks), (kit / S::KS) & 1, abort_flag))) break;
+          if (!(ok = mbar_wait(bar_acc_empty(as), ((kit / ACC_STAGES) & 1) ^ 1, abort_flag))) break;
+          tc_fence_after_sync();
+          const uint32_t k_addr = base + S::OFF_K + ks * OT::BYTES;
+#pragma unroll
+          for (int s = 0; s < OT::KSTEPS; s++)
+            umma_f16(tmem_base + as * CHUNK, smem_desc(OT::DESC, q_addr + OT::kstep_offset(s)),
+                     smem_desc(OT::DESC, k_addr + OT::kstep_offset(s)), IDESC, s > 0 ? 1u : 0u);
+          umma_commit(bar_k_empty(ks));
+          umma_commit(bar_acc_full(as));
+        }
+        if (ok) umma_commit(bar_q_empty(qs));
+      }
+    }
+  } else {
+    // ---------------- epilogue groups: thread <-> band row of the tile ----------------
+    const int grp = (warp - 2) >> 2;   // 0 or 1
+    const int quarter = warp & 3;      // TMEM lanes 32*quarter .. +31 belong to this warp
+    const int rr = quarter * 32 + lane;
+    const bool leader = (threadIdx.x == 64 + grp * EPI_THREADS);
+    const uint32_t bar_id = 1 + grp;
+    const uint32_t stage = base + S::OFF_STAGE + grp * 2 * S::STAGE_HALF;
+    const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
+    const int W = 2 * p.w + 1;
+    const int items_per_tile = paired ? p.nchunks - 1 : p.nchunks;
+    uint16_t *band = static_cast<uint16_t *>(p.band);
+    int ait = 0, iit = 0;  // accumulator stages consumed so far / work items seen so far (both groups)
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
+      const int b = tile / p.tiles_per_batch, r0 = (tile % p.tiles_per_batch) * TILE;
+      const int i = r0 + rr;
+      const int vr = min(TILE, p.M - r0);  // valid rows of this tile
+      for (int item = 0; item < items_per_tile; ++item, ++iit) {
+        const bool pair_item = paired && item == 0;
+        const int nacc = pair_item ? 2 : 1;
+        const int a0 = ait;
+        ait += nacc;
+        if ((iit & 1) != grp) continue;
+        const int as = a0 % ACC_STAGES, as2 = (a0 + 1) % ACC_STAGES;
+        const int c = pair_item ? 0 : (paired ? item : item);  // chunk index (paired: items 1.. are chunks 1..)
+        const bool staged = pair_item || ((c >= 1) && (c * CHUNK + CHUNK - 1 <= 2 * p.w));
+        if (leader) {
+          int good = mbar_wait(bar_acc_full(as), (a0 / ACC_STAGES) & 1, abort_flag) ? 1 : 0;
+          if (good && pair_item) good = mbar_wait(bar_acc_full(as2), ((a0 + 1) / ACC_STAGES) & 1, abort_flag) ? 1 : 0;
+          if (staged) bulk_wait_read<0>();  // this group's previous store has drained its staging buffer
+          epi_ok[grp] = good;
+        }
+        named_bar_sync(bar_id, EPI_THREADS);
+        if (!(ok = (epi_ok[grp] != 0))) break;
+        tc_fence_after_sync();
+        const uint32_t taddr = tmem_base + as * CHUNK + lane_sel;
+        // positions of chunk c inside the sequence: columns kk in [kk_lo, kk_hi)
+        const int p0 = r0 - p.w + p.off + c * CHUNK;
+        const int kk_lo = p.lo - p0, kk_hi = p.hi - p0;
+        const bool edge = kk_lo > 0 || kk_hi < CHUNK;
+
+        if (pair_item) {
+          // ---- merged first + last chunk ----
+          const int cl = p.nchunks - 1;
+          const uint32_t taddr_l = tmem_base + as2 * CHUNK + lane_sel;
+          const int kl_lo = kk_lo - cl * CHUNK, kl_hi = kk_hi - cl * CHUNK;
+          const bool edge_l = kl_lo > 0 || kl_hi < CHUNK;
+          const bool direct_l = (rr == vr - 1);  // last valid row: its last-chunk piece has no staging line
+          uint16_t *row_l = band + ((int64_t)b * p.M + i) * W + (cl * CHUNK - rr);
+#pragma unroll
+          for (int g = 0; g < 4; g++) {
+            uint32_t v0[32], vl[32];
+            tmem_ld_x32(taddr + g * 32, v0);
+            tmem_ld_x32(taddr_l + g * 32, vl);
+            tmem_ld_wait();
+            if (edge) mask_columns(v0, g * 32, kk_lo, kk_hi);
+            if (edge_l) mask_columns(vl, g * 32, kl_lo, kl_hi);
+            if (rr < vr) {
+#pragma unroll
+              for (int q4 = 0; q4 < 4; q4++) {
+                const int kk0 = g * 32 + q4 * 8, cg = kk0 >> 3;
+                // first chunk, row rr -> line rr, columns >= rr
+                if (kk0 >= rr) {
+                  st_shared_v4(stage_addr(stage, rr, cg), pack8<BF16>(&v0[q4 * 8]));
+                } else if (kk0 + 7 >= rr) {
+                  const uint32_t a = stage_addr(stage, rr, cg);
+#pragma unroll
+                  for (int e = 0; e < 8; e++)
+                    if (kk0 + e >= rr) st_shared_u16(a + 2 * e, pack1<BF16>(v0[q4 * 8 + e]));
+                }
+                // last chunk, row rr -> line rr + 1, columns <= rr
+                if (!direct_l) {
+                  if (kk0 + 7 <= rr) {
+                    st_shared_v4(stage_addr(stage, rr + 1, cg), pack8<BF16>(&vl[q4 * 8]));
+                  } else if (kk0 <= rr) {
+                    const uint32_t a = stage_addr(stage, rr + 1, cg);
+#pragma unroll
+                    for (int e = 0; e < 8; e++)
+                      if (kk0 + e <= rr) st_shared_u16(a + 2 * e, pack1<BF16>(vl[q4 * 8 + e]));
+                  }
+                } else {
+                  if (kk0 + 7 <= rr) {
+                    *reinterpret_cast<uint4 *>(row_l + kk0) = pack8<BF16>(&vl[q4 * 8]);
+                  } else if (kk0 <= rr) {
+#pragma unroll
+                    for (int e = 0; e < 8; e++)
+                      if (kk0 + e <= rr) row_l[kk0 + e] = pack1<BF16>(vl[q4 * 8 + e]);
+                  }
+                }
+              }
+            }
+          }
+          tc_fence_before_sync();
+          mbar_arrive(bar_acc_empty(as));
+          mbar_arrive(bar_acc_empty(as2));
+        } else if (staged) {
+          // ---- chunk wholly inside the band ----
+#pragma unroll
+          for (int g2 = 0; g2 < 2; g2++) {
+            uint32_t va[32], vb[32];
+            tmem_ld_x32(taddr + g2 * 64, va);
+            tmem_ld_x32(taddr + g2 * 64 + 32, vb);
+            tmem_ld_wait();
+            if (edge) {
+              mask_columns(va, g2 * 64, kk_lo, kk_hi);
+              mask_columns(vb, g2 * 64 + 32, kk_lo, kk_hi);
+            }
+#pragma unroll
+            for (int q4 = 0; q4 < 4; q4++) st_shared_v4(stage_addr(stage, rr, g2 * 8 + q4), pack8<BF16>(&va[q4 * 8]));
+#pragma unroll
+            for (int q4 = 0; q4 < 4; q4++) st_shared_v4(stage_addr(stage, rr, g2 * 8 + 4 + q4), pack8<BF16>(&vb[q4 * 8]));
+          }
+          tc_fence_before_sync();
+          mbar_arrive(bar_acc_empty(as));
+        } else {
+          // ---- triangular / ragged chunk of an unpaired window: predicated stores from registers.
+          // Groups of 8 columns start on 16-byte boundaries of the band tensor, so whole groups go out
+          // as one 16-byte store.
+          uint16_t *row = band + ((int64_t)b * p.M + i) * W;
+#pragma unroll
+          for (int g = 0; g < 4; g++) {
+            uint32_t v[32];
+            tmem_ld_x32(taddr + g * 32, v);
+            tmem_ld_wait();
+            if (edge) mask_columns(v, g * 32, kk_lo, kk_hi);
+            if (rr < vr) {
+#pragma unroll
+              for (int q4 = 0; q4 < 4; q4++) {
+                const int j0 = c * CHUNK + g * 32 + q4 * 8 - rr;
+                if (j0 >= 0 && j0 + 7 <= 2 * p.w) {
+                  *reinterpret_cast<uint4 *>(row + j0) = pack8<BF16>(&v[q4 * 8]);
+                } else if (j0 + 7 >= 0 && j0 <= 2 * p.w) {
+#pragma unroll
+                  for (int e = 0; e < 8; e++)
+                    if (j0 + e >= 0 && j0 + e <= 2 * p.w) row[j0 + e] = pack1<BF16>(v[q4 * 8 + e]);
+                }
+              }
+            }
+          }
+          tc_fence_before_sync();
+          mbar_arrive(bar_acc_empty(as));
+        }
+
+        if (staged) {
+          fence_proxy_async_smem();
+          named_bar_sync(bar_id, EPI_THREADS);
+          if (leader) {
+            const int x0 = r0 + c * CHUNK;  // x = i + j of the box's first column
+            tma_store_3d(&map_band, stage, x0, r0, b);
+            tma_store_3d(&map_band, stage + S::STAGE_HALF, x0 + 64, r0, b);
+            bulk_commit();
+          }
+        }
+      }
+    }
+    if (leader) bulk_wait_all();
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) atomicOr(&g_device_status, ST_NT_TIMEOUT);
+    // give copies and MMAs that may still be in flight time to land before shared and tensor memory go away
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
