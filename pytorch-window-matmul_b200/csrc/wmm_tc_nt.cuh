@@ -12,12 +12,14 @@
 //     chunk.  Only the last valid row's last-chunk piece (one row, <= 256 bytes) is written directly.
 //   * for other windows the triangular chunks are written with predicated 16-byte stores from registers.
 //
-// Warps: 0 = TMA producer, 1 = MMA issuer / TMEM owner, 2-5 and 6-9 = two epilogue groups that take
-// work items (a full chunk, or the merged first+last pair) alternately, each with its own staging
-// buffer, so conversion of one item overlaps the drain of the other.
+// Warps: 0 = TMA producer, 1 = MMA issuer / TMEM owner, 2-17 = four epilogue groups of four warps that
+// take work items (half a chunk = one 128 x 64 TMA box) round-robin, each with its own staging box: the
+// conversion is latency-bound per warp, so it needs many warps, and one group's conversion overlaps the
+// drain of the others' stores.
 
-constexpr int NT_THREADS = 320;
+constexpr int EPI_GROUPS = 4;
 constexpr int EPI_THREADS = 128;
+constexpr int NT_THREADS = 64 + EPI_GROUPS * EPI_THREADS;
 constexpr unsigned long long ST_NT_TIMEOUT = 1ull << 0;
 
 struct NtParams {
@@ -34,8 +36,8 @@ template <int NH> struct NtSmem {
   static constexpr int STAGE_HALF = TILE * 128;  // 128 lines x 64 columns x 2 bytes
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + QS * OT::BYTES;
-  static constexpr int OFF_STAGE = OFF_K + KS * OT::BYTES;  // one 32 KB buffer per epilogue group
-  static constexpr int OFF_BARS = OFF_STAGE + 2 * 2 * STAGE_HALF;
+  static constexpr int OFF_STAGE = OFF_K + KS * OT::BYTES;  // one 16 KB box per epilogue group
+  static constexpr int OFF_BARS = OFF_STAGE + EPI_GROUPS * STAGE_HALF;
   static constexpr int NBARS = 2 * QS + 2 * KS + 2 * ACC_STAGES;
   static constexpr int OFF_MISC = OFF_BARS + NBARS * 8;
   static constexpr int BYTES = OFF_MISC + 32;
@@ -57,9 +59,9 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, const uint4 &o) {
 __device__ __forceinline__ void st_shared_u16(uint32_t addr, uint16_t v) {
   asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"(v) : "memory");
 }
-// address of the 16-byte piece (line, column group cg = column / 8) of a 128 x 128 staging box
+// address of the 16-byte piece (line, column group cg = column / 8 in 0..7) of a 128-line x 64-column staging box
 __device__ __forceinline__ uint32_t stage_addr(uint32_t stage, int line, int cg) {
-  return stage + (cg >> 3) * (TILE * 128) + line * 128 + (((cg & 7) ^ (line & 7)) << 4);
+  return stage + line * 128 + ((cg ^ (line & 7)) << 4);
 }
 // zero the accumulator values of 32 columns starting at column kbase whose position is outside [kk_lo, kk_hi)
 __device__ __forceinline__ void mask_columns(uint32_t (&v)[32], int kbase, int kk_lo, int kk_hi) {
@@ -86,7 +88,7 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   auto bar_acc_empty = [&](int s) { return bars + 8u * (2 * S::QS + 2 * S::KS + ACC_STAGES + s); };
   volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + S::OFF_MISC);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(base_ptr + S::OFF_MISC + 4);
-  volatile int *epi_ok = reinterpret_cast<volatile int *>(base_ptr + S::OFF_MISC + 8);  // [2], one per group
+  volatile int *epi_ok = reinterpret_cast<volatile int *>(base_ptr + S::OFF_MISC + 8);  // one per group
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool paired = p.paired != 0;
@@ -97,10 +99,9 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::QS; s++) { mbar_init(bar_q_full(s), 1); mbar_init(bar_q_empty(s), 1); }
     for (int s = 0; s < S::KS; s++) { mbar_init(bar_k_full(s), 1); mbar_init(bar_k_empty(s), 1); }
-    for (int s = 0; s < ACC_STAGES; s++) { mbar_init(bar_acc_full(s), 1); mbar_init(bar_acc_empty(s), EPI_THREADS); }
+    for (int s = 0; s < ACC_STAGES; s++) { mbar_init(bar_acc_full(s), 1); mbar_init(bar_acc_empty(s), 2 * EPI_THREADS); }
     *abort_flag = 0;
-    epi_ok[0] = 1;
-    epi_ok[1] = 1;
+    for (int g = 0; g < EPI_GROUPS; g++) epi_ok[g] = 1;
     fence_mbar_init();
     prefetch_tmap(&map_x);
     prefetch_tmap(&map_y);
@@ -167,30 +168,33 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     }
   } else {
     // ---------------- epilogue groups: thread <-> band row of the tile ----------------
-    const int grp = (warp - 2) >> 2;   // 0 or 1
+    // A work item is HALF a chunk: 128 rows x 64 columns = one TMA box of the band.  Items go to the
+    // four groups round-robin; both halves of a chunk read the same accumulator stage.
+    const int grp = (warp - 2) >> 2;   // 0 .. EPI_GROUPS-1
     const int quarter = warp & 3;      // TMEM lanes 32*quarter .. +31 belong to this warp
     const int rr = quarter * 32 + lane;
     const bool leader = (threadIdx.x == 64 + grp * EPI_THREADS);
     const uint32_t bar_id = 1 + grp;
-    const uint32_t stage = base + S::OFF_STAGE + grp * 2 * S::STAGE_HALF;
+    const uint32_t stage = base + S::OFF_STAGE + grp * S::STAGE_HALF;
     const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
     const int W = 2 * p.w + 1;
-    const int items_per_tile = paired ? p.nchunks - 1 : p.nchunks;
+    const int items_per_tile = 2 * (paired ? p.nchunks - 1 : p.nchunks);
     uint16_t *band = static_cast<uint16_t *>(p.band);
-    int ait = 0, iit = 0;  // accumulator stages consumed so far / work items seen so far (both groups)
+    int ait = 0, iit = 0;  // accumulator stages consumed so far / half-chunk items seen so far (all groups)
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
       const int b = tile / p.tiles_per_batch, r0 = (tile % p.tiles_per_batch) * TILE;
       const int i = r0 + rr;
       const int vr = min(TILE, p.M - r0);  // valid rows of this tile
-      for (int item = 0; item < items_per_tile; ++item, ++iit) {
+      const bool rows_ok = rr < vr;
+      for (int hitem = 0; hitem < items_per_tile; ++hitem, ++iit) {
+        const int item = hitem >> 1, h = hitem & 1;
         const bool pair_item = paired && item == 0;
-        const int nacc = pair_item ? 2 : 1;
         const int a0 = ait;
-        ait += nacc;
-        if ((iit & 1) != grp) continue;
+        if (h == 1) ait += pair_item ? 2 : 1;
+        if ((iit % EPI_GROUPS) != grp) continue;
         const int as = a0 % ACC_STAGES, as2 = (a0 + 1) % ACC_STAGES;
-        const int c = pair_item ? 0 : (paired ? item : item);  // chunk index (paired: items 1.. are chunks 1..)
+        const int c = pair_item ? 0 : item;  // chunk index (with pairing, items 1.. are chunks 1..)
         const bool staged = pair_item || ((c >= 1) && (c * CHUNK + CHUNK - 1 <= 2 * p.w));
         if (leader) {
           int good = mbar_wait(bar_acc_full(as), (a0 / ACC_STAGES) & 1, abort_flag) ? 1 : 0;
@@ -209,6 +213,9 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
 
         if (pair_item) {
           // ---- merged first + last chunk ----
+          // A warp owns rows 32*quarter .. +31.  Column blocks left of its diagonal block hold only
+          // last-chunk entries of these rows, blocks right of it only first-chunk entries; the diagonal
+          // block holds both, split per lane.
           const int cl = p.nchunks - 1;
           const uint32_t taddr_l = tmem_base + as2 * CHUNK + lane_sel;
           const int kl_lo = kk_lo - cl * CHUNK, kl_hi = kk_hi - cl * CHUNK;
@@ -216,43 +223,69 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           const bool direct_l = (rr == vr - 1);  // last valid row: its last-chunk piece has no staging line
           uint16_t *row_l = band + ((int64_t)b * p.M + i) * W + (cl * CHUNK - rr);
 #pragma unroll
-          for (int g = 0; g < 4; g++) {
-            uint32_t v0[32], vl[32];
-            tmem_ld_x32(taddr + g * 32, v0);
-            tmem_ld_x32(taddr_l + g * 32, vl);
-            tmem_ld_wait();
-            if (edge) mask_columns(v0, g * 32, kk_lo, kk_hi);
-            if (edge_l) mask_columns(vl, g * 32, kl_lo, kl_hi);
-            if (rr < vr) {
+          for (int gb = 0; gb < 2; gb++) {
+            const int g = 2 * h + gb;
+            if (g < quarter) {
+              uint32_t vl[32];
+              tmem_ld_x32(taddr_l + g * 32, vl);
+              tmem_ld_wait();
+              if (edge_l) mask_columns(vl, g * 32, kl_lo, kl_hi);
+              if (rows_ok) {
 #pragma unroll
-              for (int q4 = 0; q4 < 4; q4++) {
-                const int kk0 = g * 32 + q4 * 8, cg = kk0 >> 3;
-                // first chunk, row rr -> line rr, columns >= rr
-                if (kk0 >= rr) {
-                  st_shared_v4(stage_addr(stage, rr, cg), pack8<BF16>(&v0[q4 * 8]));
-                } else if (kk0 + 7 >= rr) {
-                  const uint32_t a = stage_addr(stage, rr, cg);
-#pragma unroll
-                  for (int e = 0; e < 8; e++)
-                    if (kk0 + e >= rr) st_shared_u16(a + 2 * e, pack1<BF16>(v0[q4 * 8 + e]));
+                for (int q4 = 0; q4 < 4; q4++) {
+                  if (!direct_l)
+                    st_shared_v4(stage_addr(stage, rr + 1, gb * 4 + q4), pack8<BF16>(&vl[q4 * 8]));
+                  else
+                    *reinterpret_cast<uint4 *>(row_l + g * 32 + q4 * 8) = pack8<BF16>(&vl[q4 * 8]);
                 }
-                // last chunk, row rr -> line rr + 1, columns <= rr
-                if (!direct_l) {
-                  if (kk0 + 7 <= rr) {
-                    st_shared_v4(stage_addr(stage, rr + 1, cg), pack8<BF16>(&vl[q4 * 8]));
-                  } else if (kk0 <= rr) {
-                    const uint32_t a = stage_addr(stage, rr + 1, cg);
+              }
+            } else if (g > quarter) {
+              uint32_t v0[32];
+              tmem_ld_x32(taddr + g * 32, v0);
+              tmem_ld_wait();
+              if (edge) mask_columns(v0, g * 32, kk_lo, kk_hi);
+              if (rows_ok) {
+#pragma unroll
+                for (int q4 = 0; q4 < 4; q4++) st_shared_v4(stage_addr(stage, rr, gb * 4 + q4), pack8<BF16>(&v0[q4 * 8]));
+              }
+            } else {
+              uint32_t v0[32], vl[32];
+              tmem_ld_x32(taddr + g * 32, v0);
+              tmem_ld_x32(taddr_l + g * 32, vl);
+              tmem_ld_wait();
+              if (edge) mask_columns(v0, g * 32, kk_lo, kk_hi);
+              if (edge_l) mask_columns(vl, g * 32, kl_lo, kl_hi);
+              if (rows_ok) {
+#pragma unroll
+                for (int q4 = 0; q4 < 4; q4++) {
+                  const int kk0 = g * 32 + q4 * 8, cg = gb * 4 + q4;
+                  // first chunk, row rr -> line rr, columns >= rr
+                  if (kk0 >= rr) {
+                    st_shared_v4(stage_addr(stage, rr, cg), pack8<BF16>(&v0[q4 * 8]));
+                  } else if (kk0 + 7 >= rr) {
+                    const uint32_t a = stage_addr(stage, rr, cg);
 #pragma unroll
                     for (int e = 0; e < 8; e++)
-                      if (kk0 + e <= rr) st_shared_u16(a + 2 * e, pack1<BF16>(vl[q4 * 8 + e]));
+                      if (kk0 + e >= rr) st_shared_u16(a + 2 * e, pack1<BF16>(v0[q4 * 8 + e]));
                   }
-                } else {
-                  if (kk0 + 7 <= rr) {
-                    *reinterpret_cast<uint4 *>(row_l + kk0) = pack8<BF16>(&vl[q4 * 8]);
-                  } else if (kk0 <= rr) {
+                  // last chunk, row rr -> line rr + 1, columns <= rr
+                  if (!direct_l) {
+                    if (kk0 + 7 <= rr) {
+                      st_shared_v4(stage_addr(stage, rr + 1, cg), pack8<BF16>(&vl[q4 * 8]));
+                    } else if (kk0 <= rr) {
+                      const uint32_t a = stage_addr(stage, rr + 1, cg);
 #pragma unroll
-                    for (int e = 0; e < 8; e++)
-                      if (kk0 + e <= rr) row_l[kk0 + e] = pack1<BF16>(vl[q4 * 8 + e]);
+                      for (int e = 0; e < 8; e++)
+                        if (kk0 + e <= rr) st_shared_u16(a + 2 * e, pack1<BF16>(vl[q4 * 8 + e]));
+                    }
+                  } else {
+                    if (kk0 + 7 <= rr) {
+                      *reinterpret_cast<uint4 *>(row_l + kk0) = pack8<BF16>(&vl[q4 * 8]);
+                    } else if (kk0 <= rr) {
+#pragma unroll
+                      for (int e = 0; e < 8; e++)
+                        if (kk0 + e <= rr) row_l[kk0 + e] = pack1<BF16>(vl[q4 * 8 + e]);
+                    }
                   }
                 }
               }
@@ -262,22 +295,19 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           mbar_arrive(bar_acc_empty(as));
           mbar_arrive(bar_acc_empty(as2));
         } else if (staged) {
-          // ---- chunk wholly inside the band ----
-#pragma unroll
-          for (int g2 = 0; g2 < 2; g2++) {
-            uint32_t va[32], vb[32];
-            tmem_ld_x32(taddr + g2 * 64, va);
-            tmem_ld_x32(taddr + g2 * 64 + 32, vb);
-            tmem_ld_wait();
-            if (edge) {
-              mask_columns(va, g2 * 64, kk_lo, kk_hi);
-              mask_columns(vb, g2 * 64 + 32, kk_lo, kk_hi);
-            }
-#pragma unroll
-            for (int q4 = 0; q4 < 4; q4++) st_shared_v4(stage_addr(stage, rr, g2 * 8 + q4), pack8<BF16>(&va[q4 * 8]));
-#pragma unroll
-            for (int q4 = 0; q4 < 4; q4++) st_shared_v4(stage_addr(stage, rr, g2 * 8 + 4 + q4), pack8<BF16>(&vb[q4 * 8]));
+          // ---- half of a chunk that lies wholly inside the band ----
+          uint32_t va[32], vb[32];
+          tmem_ld_x32(taddr + h * 64, va);
+          tmem_ld_x32(taddr + h * 64 + 32, vb);
+          tmem_ld_wait();
+          if (edge) {
+            mask_columns(va, h * 64, kk_lo, kk_hi);
+            mask_columns(vb, h * 64 + 32, kk_lo, kk_hi);
           }
+#pragma unroll
+          for (int q4 = 0; q4 < 4; q4++) st_shared_v4(stage_addr(stage, rr, q4), pack8<BF16>(&va[q4 * 8]));
+#pragma unroll
+          for (int q4 = 0; q4 < 4; q4++) st_shared_v4(stage_addr(stage, rr, 4 + q4), pack8<BF16>(&vb[q4 * 8]));
           tc_fence_before_sync();
           mbar_arrive(bar_acc_empty(as));
         } else {
@@ -286,12 +316,13 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           // as one 16-byte store.
           uint16_t *row = band + ((int64_t)b * p.M + i) * W;
 #pragma unroll
-          for (int g = 0; g < 4; g++) {
+          for (int gb = 0; gb < 2; gb++) {
+            const int g = 2 * h + gb;
             uint32_t v[32];
             tmem_ld_x32(taddr + g * 32, v);
             tmem_ld_wait();
             if (edge) mask_columns(v, g * 32, kk_lo, kk_hi);
-            if (rr < vr) {
+            if (rows_ok) {
 #pragma unroll
               for (int q4 = 0; q4 < 4; q4++) {
                 const int j0 = c * CHUNK + g * 32 + q4 * 8 - rr;
@@ -313,9 +344,7 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           fence_proxy_async_smem();
           named_bar_sync(bar_id, EPI_THREADS);
           if (leader) {
-            const int x0 = r0 + c * CHUNK;  // x = i + j of the box's first column
-            tma_store_3d(&map_band, stage, x0, r0, b);
-            tma_store_3d(&map_band, stage + S::STAGE_HALF, x0 + 64, r0, b);
+            tma_store_3d(&map_band, stage, r0 + c * CHUNK + h * 64, r0, b);  // x = i + j of the box's first column
             bulk_commit();
           }
         }
