@@ -38,7 +38,7 @@ using namespace ptx;
 
 constexpr int TILE = 128;       // band rows per tile = MMA M
 constexpr int CHUNK = 128;      // positions per chunk = MMA N of band_nt
-constexpr int ACC_STAGES = 4;   // 4 x 128 TMEM columns
+constexpr int ACC_STAGES = 8;   // band_nt: 8 x 64 TMEM columns
 // Status codes OR-ed into g_device_status when a bounded wait runs out: bit 0 band_nt, bit 1 band_n / band_t.
 
 // A (128 rows x NH) 16-bit operand tile in shared memory, K-major, written by TMA with the hardware

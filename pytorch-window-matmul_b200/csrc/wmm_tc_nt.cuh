@@ -17,6 +17,7 @@
 // conversion is latency-bound per warp, so it needs many warps, and one group's conversion overlaps the
 // drain of the others' stores.
 
+constexpr int HALF = 64;        // positions per accumulator stage / per epilogue work item
 constexpr int EPI_GROUPS = 4;
 constexpr int EPI_THREADS = 128;
 constexpr int NT_THREADS = 64 + EPI_GROUPS * EPI_THREADS;
@@ -99,7 +100,7 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::QS; s++) { mbar_init(bar_q_full(s), 1); mbar_init(bar_q_empty(s), 1); }
     for (int s = 0; s < S::KS; s++) { mbar_init(bar_k_full(s), 1); mbar_init(bar_k_empty(s), 1); }
-    for (int s = 0; s < ACC_STAGES; s++) { mbar_init(bar_acc_full(s), 1); mbar_init(bar_acc_empty(s), 2 * EPI_THREADS); }
+    for (int s = 0; s < ACC_STAGES; s++) { mbar_init(bar_acc_full(s), 1); mbar_init(bar_acc_empty(s), EPI_THREADS); }
     *abort_flag = 0;
     for (int g = 0; g < EPI_GROUPS; g++) epi_ok[g] = 1;
     fence_mbar_init();
@@ -142,26 +143,49 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
+    // One accumulator stage = half a chunk (128 rows x 64 positions, 64 TMEM columns), the unit the
+    // epilogue groups consume; 8 stages.  With pairing the first and last chunk are interleaved half by
+    // half, so that each merged half-box finds both its triangles in TMEM.
     if (lane == 0) {
-      constexpr uint32_t IDESC = instr_desc_f16(BF16, false, false, TILE, CHUNK);
-      int qit = 0, kit = 0;
+      constexpr uint32_t IDESC = instr_desc_f16(BF16, false, false, TILE, HALF);
+      int qit = 0, kit = 0, ait = 0;
       bool ok = true;
+      auto half_mma = [&](uint32_t q_addr, uint32_t k_addr, int half) -> bool {
+        const int as = ait % ACC_STAGES;
+        if (!mbar_wait(bar_acc_empty(as), ((ait / ACC_STAGES) & 1) ^ 1, abort_flag)) return false;
+        tc_fence_after_sync();
+        const uint32_t b_addr = k_addr + half * HALF * OT::SW_BYTES;  // rows 64*half .. of every box
+#pragma unroll
+        for (int s = 0; s < OT::KSTEPS; s++)
+          umma_f16(tmem_base + as * HALF, smem_desc(OT::DESC, q_addr + OT::kstep_offset(s)),
+                   smem_desc(OT::DESC, b_addr + OT::kstep_offset(s)), IDESC, s > 0 ? 1u : 0u);
+        umma_commit(bar_acc_full(as));
+        ++ait;
+        return true;
+      };
       for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x, ++qit) {
         const int qs = qit % S::QS;
         if (!(ok = mbar_wait(bar_q_full(qs), (qit / S::QS) & 1, abort_flag))) break;
         const uint32_t q_addr = base + S::OFF_Q + qs * OT::BYTES;
-        for (int k = 0; k < p.nchunks; ++k, ++kit) {
-          const int ks = kit % S::KS, as = kit % ACC_STAGES;
+        int k = 0;
+        if (paired) {
+          const int ks0 = kit % S::KS, ks1 = (kit + 1) % S::KS;
+          if (!(ok = mbar_wait(bar_k_full(ks0), (kit / S::KS) & 1, abort_flag))) break;
+          if (!(ok = mbar_wait(bar_k_full(ks1), ((kit + 1) / S::KS) & 1, abort_flag))) break;
+          const uint32_t k0_addr = base + S::OFF_K + ks0 * OT::BYTES, k1_addr = base + S::OFF_K + ks1 * OT::BYTES;
+          for (int half = 0; ok && half < 2; half++) ok = half_mma(q_addr, k0_addr, half) && half_mma(q_addr, k1_addr, half);
+          if (!ok) break;
+          umma_commit(bar_k_empty(ks0));
+          umma_commit(bar_k_empty(ks1));
+          kit += 2;
+          k = 2;
+        }
+        for (; k < p.nchunks; ++k, ++kit) {
+          const int ks = kit % S::KS;
           if (!(ok = mbar_wait(bar_k_full(ks), (kit / S::KS) & 1, abort_flag))) break;
-          if (!(ok = mbar_wait(bar_acc_empty(as), ((kit / ACC_STAGES) & 1) ^ 1, abort_flag))) break;
-          tc_fence_after_sync();
           const uint32_t k_addr = base + S::OFF_K + ks * OT::BYTES;
-#pragma unroll
-          for (int s = 0; s < OT::KSTEPS; s++)
-            umma_f16(tmem_base + as * CHUNK, smem_desc(OT::DESC, q_addr + OT::kstep_offset(s)),
-                     smem_desc(OT::DESC, k_addr + OT::kstep_offset(s)), IDESC, s > 0 ? 1u : 0u);
+          if (!(ok = half_mma(q_addr, k_addr, 0) && half_mma(q_addr, k_addr, 1))) break;
           umma_commit(bar_k_empty(ks));
-          umma_commit(bar_acc_full(as));
         }
         if (ok) umma_commit(bar_q_empty(qs));
       }
@@ -191,7 +215,7 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         const int item = hitem >> 1, h = hitem & 1;
         const bool pair_item = paired && item == 0;
         const int a0 = ait;
-        if (h == 1) ait += pair_item ? 2 : 1;
+        ait += pair_item ? 2 : 1;
         if ((iit % EPI_GROUPS) != grp) continue;
         const int as = a0 % ACC_STAGES, as2 = (a0 + 1) % ACC_STAGES;
         const int c = pair_item ? 0 : item;  // chunk index (with pairing, items 1.. are chunks 1..)
@@ -205,7 +229,7 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         named_bar_sync(bar_id, EPI_THREADS);
         if (!(ok = (epi_ok[grp] != 0))) break;
         tc_fence_after_sync();
-        const uint32_t taddr = tmem_base + as * CHUNK + lane_sel;
+        const uint32_t taddr = tmem_base + as * HALF + lane_sel;  // columns 64*h .. of chunk c
         // positions of chunk c inside the sequence: columns kk in [kk_lo, kk_hi)
         const int p0 = r0 - p.w + p.off + c * CHUNK;
         const int kk_lo = p.lo - p0, kk_hi = p.hi - p0;
@@ -217,7 +241,7 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           // last-chunk entries of these rows, blocks right of it only first-chunk entries; the diagonal
           // block holds both, split per lane.
           const int cl = p.nchunks - 1;
-          const uint32_t taddr_l = tmem_base + as2 * CHUNK + lane_sel;
+          const uint32_t taddr_l = tmem_base + as2 * HALF + lane_sel;
           const int kl_lo = kk_lo - cl * CHUNK, kl_hi = kk_hi - cl * CHUNK;
           const bool edge_l = kl_lo > 0 || kl_hi < CHUNK;
           const bool direct_l = (rr == vr - 1);  // last valid row: its last-chunk piece has no staging line
@@ -227,7 +251,7 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             const int g = 2 * h + gb;
             if (g < quarter) {
               uint32_t vl[32];
-              tmem_ld_x32(taddr_l + g * 32, vl);
+              tmem_ld_x32(taddr_l + gb * 32, vl);
               tmem_ld_wait();
               if (edge_l) mask_columns(vl, g * 32, kl_lo, kl_hi);
               if (rows_ok) {
@@ -241,7 +265,7 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
               }
             } else if (g > quarter) {
               uint32_t v0[32];
-              tmem_ld_x32(taddr + g * 32, v0);
+              tmem_ld_x32(taddr + gb * 32, v0);
               tmem_ld_wait();
               if (edge) mask_columns(v0, g * 32, kk_lo, kk_hi);
               if (rows_ok) {
@@ -249,44 +273,45 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 for (int q4 = 0; q4 < 4; q4++) st_shared_v4(stage_addr(stage, rr, gb * 4 + q4), pack8<BF16>(&v0[q4 * 8]));
               }
             } else {
+              // diagonal block: line rr takes columns >= rr from this thread's first-chunk row and
+              // columns < rr from the last-chunk row of the thread one lane below (row rr - 1); lane 31
+              // also writes its own last-chunk row, which is all of line rr + 1 within this block.
               uint32_t v0[32], vl[32];
-              tmem_ld_x32(taddr + g * 32, v0);
-              tmem_ld_x32(taddr_l + g * 32, vl);
+              tmem_ld_x32(taddr + gb * 32, v0);
+              tmem_ld_x32(taddr_l + gb * 32, vl);
               tmem_ld_wait();
               if (edge) mask_columns(v0, g * 32, kk_lo, kk_hi);
               if (edge_l) mask_columns(vl, g * 32, kl_lo, kl_hi);
+              uint32_t m[16], pl[16];
+#pragma unroll
+              for (int k2 = 0; k2 < 16; k2++) {
+                pl[k2] = pack2<BF16>(vl[2 * k2], vl[2 * k2 + 1]);
+                const uint32_t own = pack2<BF16>(v0[2 * k2], v0[2 * k2 + 1]);
+                const uint32_t up = __shfl_up_sync(0xffffffffu, pl[k2], 1);
+                m[k2] = (2 * k2 >= lane) ? own : ((2 * k2 + 1 < lane) ? up : ((up & 0x0000ffffu) | (own & 0xffff0000u)));
+              }
               if (rows_ok) {
 #pragma unroll
-                for (int q4 = 0; q4 < 4; q4++) {
-                  const int kk0 = g * 32 + q4 * 8, cg = gb * 4 + q4;
-                  // first chunk, row rr -> line rr, columns >= rr
-                  if (kk0 >= rr) {
-                    st_shared_v4(stage_addr(stage, rr, cg), pack8<BF16>(&v0[q4 * 8]));
-                  } else if (kk0 + 7 >= rr) {
-                    const uint32_t a = stage_addr(stage, rr, cg);
+                for (int q4 = 0; q4 < 4; q4++)
+                  st_shared_v4(stage_addr(stage, rr, gb * 4 + q4), make_uint4(m[4 * q4], m[4 * q4 + 1], m[4 * q4 + 2], m[4 * q4 + 3]));
+                if (direct_l) {
+                  // the last valid row of the tile: columns 32*quarter .. rr of its last-chunk row go
+                  // straight to the band (lane + 1 values)
 #pragma unroll
-                    for (int e = 0; e < 8; e++)
-                      if (kk0 + e >= rr) st_shared_u16(a + 2 * e, pack1<BF16>(v0[q4 * 8 + e]));
-                  }
-                  // last chunk, row rr -> line rr + 1, columns <= rr
-                  if (!direct_l) {
+                  for (int q4 = 0; q4 < 4; q4++) {
+                    const int kk0 = g * 32 + q4 * 8;
                     if (kk0 + 7 <= rr) {
-                      st_shared_v4(stage_addr(stage, rr + 1, cg), pack8<BF16>(&vl[q4 * 8]));
-                    } else if (kk0 <= rr) {
-                      const uint32_t a = stage_addr(stage, rr + 1, cg);
-#pragma unroll
-                      for (int e = 0; e < 8; e++)
-                        if (kk0 + e <= rr) st_shared_u16(a + 2 * e, pack1<BF16>(vl[q4 * 8 + e]));
-                    }
-                  } else {
-                    if (kk0 + 7 <= rr) {
-                      *reinterpret_cast<uint4 *>(row_l + kk0) = pack8<BF16>(&vl[q4 * 8]);
+                      *reinterpret_cast<uint4 *>(row_l + kk0) = make_uint4(pl[4 * q4], pl[4 * q4 + 1], pl[4 * q4 + 2], pl[4 * q4 + 3]);
                     } else if (kk0 <= rr) {
 #pragma unroll
                       for (int e = 0; e < 8; e++)
-                        if (kk0 + e <= rr) row_l[kk0 + e] = pack1<BF16>(vl[q4 * 8 + e]);
+                        if (kk0 + e <= rr) row_l[kk0 + e] = (uint16_t)(pl[4 * q4 + (e >> 1)] >> ((e & 1) * 16));
                     }
                   }
+                } else if (lane == 31) {
+#pragma unroll
+                  for (int q4 = 0; q4 < 4; q4++)
+                    st_shared_v4(stage_addr(stage, rr + 1, gb * 4 + q4), make_uint4(pl[4 * q4], pl[4 * q4 + 1], pl[4 * q4 + 2], pl[4 * q4 + 3]));
                 }
               }
             }
@@ -297,8 +322,8 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         } else if (staged) {
           // ---- half of a chunk that lies wholly inside the band ----
           uint32_t va[32], vb[32];
-          tmem_ld_x32(taddr + h * 64, va);
-          tmem_ld_x32(taddr + h * 64 + 32, vb);
+          tmem_ld_x32(taddr, va);
+          tmem_ld_x32(taddr + 32, vb);
           tmem_ld_wait();
           if (edge) {
             mask_columns(va, h * 64, kk_lo, kk_hi);
@@ -319,7 +344,7 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           for (int gb = 0; gb < 2; gb++) {
             const int g = 2 * h + gb;
             uint32_t v[32];
-            tmem_ld_x32(taddr + g * 32, v);
+            tmem_ld_x32(taddr + gb * 32, v);
             tmem_ld_wait();
             if (edge) mask_columns(v, g * 32, kk_lo, kk_hi);
             if (rows_ok) {
