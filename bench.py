@@ -252,17 +252,26 @@ def run_ours(args, torch):
     ga = torch.empty_like(a)
     o, gv, gq, gkt = (torch.empty(Bl, M, N, dtype=dtype, device=dev) for _ in range(4))
 
+    kd = ktd.transpose(-1, -2)  # K as the (B,N,M) tensor the operators take
+    # the four native calls of the reference's module = one step (5 kernel launches)
+    ops = [
+        lambda: impl.band_nt(qd, ktd, w, out=a),                                        # window forward
+        lambda: impl.band_n(a, vd, w, out=o),                                           # unwindow forward
+        lambda: impl.unwindow_matmul_backward(a, vd, w, god, out=(ga, gv)),             # grad_A, grad_V
+        lambda: impl.window_matmul_backward(qd, kd, w, ga, out=(gq, gkt)),              # grad_Q, grad_K (one launch)
+    ]
+    launches_per_step = 5
+    # (name, call, algorithmic bytes per band row / e): per-kernel durations for the roofline
     kernels = [
-        ("window_fwd band_nt", lambda: impl.band_nt(qd, ktd, w, out=a), 2 * N + W),
-        ("unwindow_fwd band_n", lambda: impl.band_n(a, vd, w, out=o), 2 * N + W),
+        ("window_fwd band_nt", ops[0], 2 * N + W),
+        ("unwindow_fwd band_n", ops[1], 2 * N + W),
         ("unwindow_bwd grad_A band_nt", lambda: impl.band_nt(god, vd, w, out=ga), 2 * N + W),
         ("unwindow_bwd grad_V band_t", lambda: impl.band_t(a, god, w, out=gv), 2 * N + W),
-        ("window_bwd grad_Q band_n", lambda: impl.band_n(ga, ktd, w, out=gq), 2 * N + W),
-        ("window_bwd grad_K band_t", lambda: impl.band_t(ga, qd, w, out=gkt), 2 * N + W),
+        ("window_bwd grad_Q+grad_K band_n+band_t", ops[3], 4 * N + W),
     ]
 
     def step():
-        for _, fn, _ in kernels:
+        for fn in ops:
             fn()
 
     stream = torch.cuda.Stream(device=dev)
@@ -300,7 +309,7 @@ def run_ours(args, torch):
             stream.synchronize()
         barrier()
         elapsed_ms = ev0.elapsed_time(ev1)
-        launches = (N_.launch_count() - launches0) if graph is None else args.steps * len(kernels)
+        launches = (N_.launch_count() - launches0) if graph is None else args.steps * launches_per_step
 
         # ---- per-kernel durations (for the roofline of the dominant kernel) ----
         per_kernel = {}
@@ -390,7 +399,7 @@ def run_ours(args, torch):
             "config": {
                 "workload": workload_name(args.workload), "batch_per_gpu": per,
                 "l2": "no flush: one step touches %.0f MB per GPU, larger than the 126 MB L2" % (total_bytes / world / 1e6),
-                "launch": "cuda graph of 6 kernels" if graph is not None else "6 stream launches",
+                "launch": "cuda graph of %d kernels" % launches_per_step if graph is not None else "%d stream launches" % launches_per_step,
                 "k_layout": "transposed view of (B,M,N)",
             },
             "step_roofline": {

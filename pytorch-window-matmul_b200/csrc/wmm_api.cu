@@ -245,6 +245,15 @@ int wmm_window_bwd(const wmm_operand *q, const wmm_operand *kt, const void *grad
   if (sq < 0) return sq;
   const int sk = build(wmm::BAND_T, pk, q, nullptr, grad_band, nullptr, grad_kt, g, dtype, flags);
   if (sk < 0) return sk;
+  if (sq == WMM_OK && sk == WMM_OK && wants_tensor(wmm::BAND_N, pq) && wants_tensor(wmm::BAND_T, pk) &&
+      wmm::tensor_fused_pair_eligible(pq, pk)) {
+    // both passes over grad_A in one launch: the band is read from HBM once
+    int launches = 0;
+    cudaError_t e = wmm::launch_tensor_fused_pair(pq, pk, (cudaStream_t)stream, &launches);
+    g_launches.fetch_add((uint64_t)launches, std::memory_order_relaxed);
+    if (e != cudaSuccess) return fail(WMM_ERR_CUDA, "CUDA error launching the fused window backward: %s", cudaGetErrorString(e));
+    return WMM_OK;
+  }
   if (sq == WMM_OK)
     if (int s = dispatch(wmm::BAND_N, pq, stream)) return s;
   if (sk == WMM_OK)

@@ -35,6 +35,10 @@ cudaError_t launch_generic(Primitive prim, const Problem &p, cudaStream_t stream
 // alignment; `launch_tensor` must only be called when it holds.
 bool tensor_eligible(Primitive prim, const Problem &p);
 cudaError_t launch_tensor(Primitive prim, const Problem &p, cudaStream_t stream, int *launches);
+// band_n and band_t over the same band in ONE launch (the band is fetched from HBM once): `pn` and `pt`
+// are the two problems; eligibility includes that they share band, geometry and dtype.
+bool tensor_fused_pair_eligible(const Problem &pn, const Problem &pt);
+cudaError_t launch_tensor_fused_pair(const Problem &pn, const Problem &pt, cudaStream_t stream, int *launches);
 
 // Device-side status word: a kernel that abandons a bounded wait ORs a code into it.  Synchronises the
 // current device, copies the word out and optionally clears it.

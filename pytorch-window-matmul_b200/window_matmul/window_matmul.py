@@ -111,10 +111,11 @@ def window_matmul_forward(src: torch.Tensor, other: torch.Tensor, window_size: i
     return band_nt(src, other.transpose(-1, -2), window_size)
 
 
-def window_matmul_backward(src, other, window_size, grad_output, need=(True, True)):
+def window_matmul_backward(src, other, window_size, grad_output, need=(True, True), out=None):
     """window_matmul.cpp:80-85 -> window_matmul_bw_cuda (window_matmul_cuda.cu:272-319).
     Returns (grad_src (B,M,N), grad_other (B,N,M)); like the reference's CUDA path, grad_other is a
-    transposed view of a contiguous (B,M,N) buffer (window_matmul_cuda.cu:318)."""
+    transposed view of a contiguous (B,M,N) buffer (window_matmul_cuda.cu:318).  `out` may give
+    preallocated (grad_src (B,M,N), grad_other^T (B,M,N)) buffers."""
     _require_cuda(src, other, grad_output)
     _mismatch(src.dim() == 3 and other.dim() == 3 and grad_output.dim() == 3)
     _mismatch(src.size(0) == other.size(0) and src.size(1) == other.size(2) and src.size(2) == other.size(1))
@@ -124,8 +125,8 @@ def window_matmul_backward(src, other, window_size, grad_output, need=(True, Tru
     src = _addressable(src)
     B, M, Nn = src.shape
     if need[0] and need[1]:
-        gq = torch.empty((B, M, Nn), dtype=src.dtype, device=src.device)
-        gkt = torch.empty((B, M, Nn), dtype=src.dtype, device=src.device)
+        gq = torch.empty((B, M, Nn), dtype=src.dtype, device=src.device) if out is None else out[0]
+        gkt = torch.empty((B, M, Nn), dtype=src.dtype, device=src.device) if out is None else out[1]
         g = N.geometry(B, M, Nn, window_size)
         with torch.cuda.device(src.device):
             N.check(N.lib.wmm_window_bwd(N.operand(src), N.operand(kt), grad_output.data_ptr(), N.operand(gq),
@@ -145,7 +146,7 @@ def unwindow_matmul_forward(src: torch.Tensor, other: torch.Tensor, window_size:
     return band_n(src, other, window_size)
 
 
-def unwindow_matmul_backward(src, other, window_size, grad_output, need=(True, True)):
+def unwindow_matmul_backward(src, other, window_size, grad_output, need=(True, True), out=None):
     """window_matmul.cpp:93-98 -> unwindow_matmul_bw_cuda (window_matmul_cuda.cu:360-416).
     Returns (grad_src (B,M,2w+1), grad_other (B,M,N))."""
     _require_cuda(src, other, grad_output)
@@ -156,8 +157,8 @@ def unwindow_matmul_backward(src, other, window_size, grad_output, need=(True, T
     other, grad_output = _addressable(other), _addressable(grad_output)
     B, M, Nn = other.shape
     if need[0] and need[1]:
-        ga = torch.empty((B, M, 2 * window_size + 1), dtype=src.dtype, device=src.device)
-        gv = torch.empty((B, M, Nn), dtype=src.dtype, device=src.device)
+        ga = torch.empty((B, M, 2 * window_size + 1), dtype=src.dtype, device=src.device) if out is None else out[0]
+        gv = torch.empty((B, M, Nn), dtype=src.dtype, device=src.device) if out is None else out[1]
         g = N.geometry(B, M, Nn, window_size)
         with torch.cuda.device(src.device):
             N.check(N.lib.wmm_unwindow_bwd(src.data_ptr(), N.operand(other), N.operand(grad_output), ga.data_ptr(),

@@ -145,6 +145,29 @@ def test_band_nt_tensor_on_a_sequence_shard(wm, shape):
         H.assert_lowp_close(a, want[:, m0:m0 + Ml], "shard %d" % r)
 
 
+@pytest.mark.parametrize("shape", [s for s in SHAPES if s[3] % 8 == 0])
+def test_window_backward_fused_tensor(wm, shape):
+    """grad_Q and grad_K from one launch over grad_A (both passes share the band tiles through L2)."""
+    from window_matmul import _native as N
+
+    B, M, Nn, w = shape
+    dtype = torch.bfloat16
+    d = _inputs(shape, dtype)
+    want_gq, want_gk = H.oracle.window_matmul_backward(d["q"], np.ascontiguousarray(d["kt"].transpose(0, 2, 1)), w, d["g_band"])
+    q, kt, g_band = (H.to_dev(d[x], dtype) for x in ("q", "kt", "g_band"))
+    old = wm.set_flags(N.FLAG_REQUIRE_TENSOR)
+    try:
+        before = N.launch_count()
+        gq, gk = wm.window_matmul_backward(q, kt.transpose(-1, -2), w, g_band)
+        assert N.launch_count() - before == 1
+    finally:
+        wm.set_flags(old)
+    torch.cuda.synchronize()
+    assert N.device_status() == 0
+    H.assert_lowp_close(gq, want_gq, "grad_q %s" % (shape,))
+    H.assert_lowp_close(gk, want_gk, "grad_k %s" % (shape,))
+
+
 def test_ineligible_problems_are_reported_not_faked(wm):
     from window_matmul import _native as N
 
