@@ -113,7 +113,8 @@ int dispatch(wmm::Primitive prim, const wmm::Problem &p, void *stream) {
                          : wmm::launch_generic(prim, p, (cudaStream_t)stream, &launches);
   g_launches.fetch_add((uint64_t)launches, std::memory_order_relaxed);
   if (e != cudaSuccess)
-    return fail(WMM_ERR_CUDA, "CUDA error launching primitive %d: %s", (int)prim, cudaGetErrorString(e));
+    return fail(WMM_ERR_CUDA, "CUDA error launching primitive %d: %s [%s]", (int)prim, cudaGetErrorString(e),
+                tensor ? wmm::launch_detail() : "generic kernel launch");
   return WMM_OK;
 }
 
@@ -251,7 +252,8 @@ int wmm_window_bwd(const wmm_operand *q, const wmm_operand *kt, const void *grad
     int launches = 0;
     cudaError_t e = wmm::launch_tensor_fused_pair(pq, pk, (cudaStream_t)stream, &launches);
     g_launches.fetch_add((uint64_t)launches, std::memory_order_relaxed);
-    if (e != cudaSuccess) return fail(WMM_ERR_CUDA, "CUDA error launching the fused window backward: %s", cudaGetErrorString(e));
+    if (e != cudaSuccess)
+      return fail(WMM_ERR_CUDA, "CUDA error launching the fused window backward: %s [%s]", cudaGetErrorString(e), wmm::launch_detail());
     return WMM_OK;
   }
   if (sq == WMM_OK)

@@ -40,6 +40,11 @@ cudaError_t launch_tensor(Primitive prim, const Problem &p, cudaStream_t stream,
 bool tensor_fused_pair_eligible(const Problem &pn, const Problem &pt);
 cudaError_t launch_tensor_fused_pair(const Problem &pn, const Problem &pt, cudaStream_t stream, int *launches);
 
+// Launchers describe a failure (which step, which driver code) here; the API layer appends it to the
+// error string of the calling thread.
+void set_launch_detail(const char *fmt, ...);
+const char *launch_detail();
+
 // Device-side status word: a kernel that abandons a bounded wait ORs a code into it.  Synchronises the
 // current device, copies the word out and optionally clears it.
 cudaError_t read_device_status(unsigned long long *word, bool clear);

@@ -13,6 +13,8 @@
 // Warp roles (persistent CTAs, one per SM, tiles taken round-robin with the sequence index fastest so
 // that neighbouring CTAs share their halo rows in L2): warp 0 = TMA producer, warp 1 = MMA issuer and
 // TMEM owner, warps 2-5 = epilogue (TMEM -> registers -> global / staging + TMA store).
+#include <cstdarg>
+#include <cstdio>
 #include <mutex>
 
 #include "wmm_common.cuh"
@@ -31,6 +33,17 @@ cudaError_t read_device_status(unsigned long long *word, bool clear) {
   }
   return e;
 }
+
+namespace {
+thread_local char tls_detail[256] = "";
+}
+void set_launch_detail(const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(tls_detail, sizeof(tls_detail), fmt, ap);
+  va_end(ap);
+}
+const char *launch_detail() { return tls_detail; }
 
 namespace {
 
@@ -129,10 +142,13 @@ bool make_operand_map(CUtensorMap *m, bool bf16, const void *data, int cols, int
   const cuuint64_t strides[2] = {(cuuint64_t)stride_r * 2, (cuuint64_t)(batch > 1 ? stride_b : (int64_t)rows * stride_r) * 2};
   const cuuint32_t box[3] = {(cuuint32_t)boxk, 128, 1};
   const cuuint32_t estr[3] = {1, 1, 1};
-  return encode_fn()(m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
-                     const_cast<void *>(data), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     swizzle_for(boxk * 2), CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  const CUresult r = encode_fn()(m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                                const_cast<void *>(data), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                swizzle_for(boxk * 2), CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    set_launch_detail("cuTensorMapEncodeTiled(operand %p, dims %d x %d x %d, strides %lld / %lld elements) returned %d", data, cols,
+                      rows, batch, (long long)stride_r, (long long)stride_b, (int)r);
+  return r == CUDA_SUCCESS;
 }
 
 // The band as a pitched matrix: x = i + j in [0, M + 2w), row i with pitch 2w elements, batch with
@@ -143,10 +159,12 @@ bool make_band_map(CUtensorMap *m, bool bf16, const void *band, int M, int w, in
   const cuuint64_t strides[2] = {(cuuint64_t)(2 * w) * 2, (cuuint64_t)M * (2ull * w + 1) * 2};
   const cuuint32_t box[3] = {64, 128, 1};
   const cuuint32_t estr[3] = {1, 1, 1};
-  return encode_fn()(m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
-                     const_cast<void *>(band), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  const CUresult r = encode_fn()(m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                                const_cast<void *>(band), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    set_launch_detail("cuTensorMapEncodeTiled(band %p, rows %d, window %d, batch %d) returned %d", band, M, w, batch, (int)r);
+  return r == CUDA_SUCCESS;
 }
 
 bool operand_tma_ok(const void *data, int64_t sb, int64_t sr, int64_t sc, int batch) {
@@ -158,10 +176,6 @@ bool band_tma_ok(const void *band, int M, int w) { return aligned16(band) && (w 
 template <bool BF16, int NH> cudaError_t launch_nt(const Problem &p, cudaStream_t stream) {
   using S = NtSmem<NH>;
   using OT = KMajorTile<NH>;
-  CUtensorMap mx, my, mb;
-  if (!make_operand_map(&mx, BF16, p.a, NH, p.M, p.B, p.a_sr, p.a_sb, OT::BOXK) ||
-      !make_operand_map(&my, BF16, p.b, NH, p.Mo, p.B, p.b_sr, p.b_sb, OT::BOXK) || !make_band_map(&mb, BF16, p.o, p.M, p.w, p.B))
-    return cudaErrorInvalidValue;
   NtParams k;
   k.B = p.B; k.M = p.M; k.w = p.w; k.off = p.off; k.lo = p.lo; k.hi = p.hi;
   k.tiles_per_batch = (p.M + TILE - 1) / TILE;
@@ -172,8 +186,18 @@ template <bool BF16, int NH> cudaError_t launch_nt(const Problem &p, cudaStream_
   auto kern = band_nt_tc_kernel<BF16, NH>;
   // the attribute is per device; setting it on every call is cheap and needs no per-device cache
   cudaError_t attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::ALLOC);
-  if (attr_err != cudaSuccess) return attr_err;
+  if (attr_err != cudaSuccess) {
+    set_launch_detail("cudaFuncSetAttribute(band_nt, %d bytes of shared memory)", S::ALLOC);
+    return attr_err;
+  }
+  // The runtime call above has bound this thread to the device's primary context; the driver entry point
+  // used for the tensor maps needs a current context (a fresh thread, e.g. an autograd worker, has none).
+  CUtensorMap mx, my, mb;
+  if (!make_operand_map(&mx, BF16, p.a, NH, p.M, p.B, p.a_sr, p.a_sb, OT::BOXK) ||
+      !make_operand_map(&my, BF16, p.b, NH, p.Mo, p.B, p.b_sr, p.b_sb, OT::BOXK) || !make_band_map(&mb, BF16, p.o, p.M, p.w, p.B))
+    return cudaErrorInvalidValue;
   const int grid = k.total_tiles < sm_count() ? k.total_tiles : sm_count();
+  set_launch_detail("band_nt launch, grid %d", grid);
   kern<<<grid, NT_THREADS, S::ALLOC, stream>>>(mx, my, mb, k);
   return cudaGetLastError();
 }
@@ -183,10 +207,22 @@ template <bool BF16, int NH> cudaError_t launch_nt(const Problem &p, cudaStream_
 template <bool BF16, int NH, int MODE> cudaError_t launch_mm(const Problem &p, const Problem *pt, cudaStream_t stream) {
   using S = MmSmem<NH>;
   using OT = KMajorTile<NH>;
-  CUtensorMap mband, mother0, mout0, mother1, mout1;
   const bool tr = MODE == 1;
   const int out_rows = tr ? p.Mo : p.M;
   const int other_rows = tr ? p.M : p.Mo;
+  MmParams k;
+  k.B = p.B; k.M = p.M; k.Mo = p.Mo; k.w = p.w; k.off = p.off; k.lo = p.lo; k.hi = p.hi;
+  k.tiles_per_batch = (out_rows + TILE - 1) / TILE;
+  k.total_tiles = k.tiles_per_batch * p.B;
+  k.nchunks = (TILE + 2 * p.w + 127) / 128;
+  auto kern = band_mm_tc_kernel<BF16, NH, MODE>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::ALLOC);
+  if (e != cudaSuccess) {
+    set_launch_detail("cudaFuncSetAttribute(band_mm mode %d, %d bytes of shared memory)", MODE, S::ALLOC);
+    return e;
+  }
+  // (the tensor maps need the current context the runtime call above has bound to this thread)
+  CUtensorMap mband, mother0, mout0, mother1, mout1;
   if (!make_band_map(&mband, BF16, p.a, p.M, p.w, p.B) ||
       !make_operand_map(&mother0, BF16, p.b, NH, other_rows, p.B, p.b_sr, p.b_sb, OT::BOXK) ||
       !make_operand_map(&mout0, BF16, p.o, NH, out_rows, p.B, p.o_sr, p.o_sb, OT::BOXK))
@@ -199,16 +235,9 @@ template <bool BF16, int NH, int MODE> cudaError_t launch_mm(const Problem &p, c
     mother1 = mother0;
     mout1 = mout0;
   }
-  MmParams k;
-  k.B = p.B; k.M = p.M; k.Mo = p.Mo; k.w = p.w; k.off = p.off; k.lo = p.lo; k.hi = p.hi;
-  k.tiles_per_batch = (out_rows + TILE - 1) / TILE;
-  k.total_tiles = k.tiles_per_batch * p.B;
-  k.nchunks = (TILE + 2 * p.w + 127) / 128;
-  auto kern = band_mm_tc_kernel<BF16, NH, MODE>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::ALLOC);
-  if (e != cudaSuccess) return e;
   const int items = MODE == 2 ? 2 * k.total_tiles : k.total_tiles;
   const int grid = items < sm_count() ? items : sm_count();
+  set_launch_detail("band_mm mode %d launch, grid %d", MODE, grid);
   kern<<<grid, MM_THREADS, S::ALLOC, stream>>>(mband, mother0, mout0, mother1, mout1, k);
   return cudaGetLastError();
 }

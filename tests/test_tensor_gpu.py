@@ -177,3 +177,29 @@ def test_ineligible_problems_are_reported_not_faked(wm):
     q = torch.randn(2, 64, 64, device="cuda", dtype=torch.float32)  # fp32 stays on the exact-order kernels
     with pytest.raises(RuntimeError, match="UNSUPPORTED"):
         wm.band_nt(q, q, 8, flags=N.FLAG_REQUIRE_TENSOR)
+
+
+def test_tensor_kernels_from_a_fresh_thread(wm):
+    """A thread that has made no CUDA call yet (an autograd worker, a thread pool) has no current context;
+    the launcher must bind one before it builds its tensor maps."""
+    import threading
+
+    from window_matmul import _native as N
+
+    q = torch.randn(2, 256, 64, device="cuda", dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    result = {}
+
+    def work():
+        try:
+            result["a"] = wm.band_nt(q, q, 64, flags=N.FLAG_REQUIRE_TENSOR)
+            result["o"] = wm.band_n(result["a"], q, 64, flags=N.FLAG_REQUIRE_TENSOR)
+        except Exception as e:  # noqa: BLE001
+            result["error"] = e
+
+    t = threading.Thread(target=work)
+    t.start()
+    t.join()
+    torch.cuda.synchronize()
+    assert "error" not in result, result.get("error")
+    assert torch.equal(result["a"], wm.band_nt(q, q, 64, flags=N.FLAG_REQUIRE_TENSOR))
