@@ -1,0 +1,185 @@
+"""Multi-GPU forms of the two operators: one process per GPU, `torch.distributed` for the plumbing.
+
+Batch sharding needs nothing from this module: every (batch x head) entry is independent in all six
+contractions, so each rank calls `window_matmul` / `unwindow_matmul` on its own slice and no data moves.
+
+Sequence sharding (long M): rank r owns rows [r*Ml, (r+1)*Ml) of Q, K, V, A and O.  A band row reaches w
+positions to either side, so
+  * forward: each rank receives the last w rows of K^T (resp. V) from rank r-1 and the first w rows from
+    rank r+1 (zeros at the ends of the global sequence) and runs the primitives on local rows + halo
+    (`other_rows = Ml + 2w`, `other_off = w`, and `seq_lo/seq_hi` clipping at the global ends);
+  * backward: grad_Q and grad_A reuse those halos; grad_K / grad_V rows within w of a shard edge also
+    receive contributions from the neighbour's band rows.  Each rank computes partial rows for its halo
+    positions from its own band rows (`band_t` with `other_rows = Ml + 2w`) and SENDS them to the neighbour,
+    which adds them (reverse halo).  Band rows never cross ranks.
+Only neighbours talk (isend/irecv pairs); there is no collective on the data path and no device-side wait
+on a peer.  Requires Ml >= w.
+
+The reference has no multi-GPU code; the single-GPU semantics are those of
+window_matmul/window_matmul.py:30-40 and :66-76, and `tests/test_sharded.py` checks that the sharded
+operators reproduce them (forward and gradients) on world_size 2 and 3.
+"""
+import importlib
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+# the submodule, not the function of the same name that the package exports
+_ops = importlib.import_module(__package__ + ".window_matmul")
+
+
+class _Primitives:
+    """The three primitives the sharded operators are built on.  Tests on CPU ranks replace this object
+    with a checker implementation; the product always uses the CUDA kernels."""
+
+    band_nt = staticmethod(_ops.band_nt)
+    band_n = staticmethod(_ops.band_n)
+    band_t = staticmethod(_ops.band_t)
+
+
+primitives = _Primitives()
+
+
+def _neighbours(group) -> Tuple[int, int, Optional[int], Optional[int]]:
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    lo = dist.get_global_rank(group, rank - 1) if (group is not None and rank > 0) else (rank - 1 if rank > 0 else None)
+    hi = dist.get_global_rank(group, rank + 1) if (group is not None and rank < world - 1) else (rank + 1 if rank < world - 1 else None)
+    return rank, world, lo, hi
+
+
+def exchange_halo(x: torch.Tensor, window: int, group=None) -> torch.Tensor:
+    """x (B, Ml, N) local rows -> (B, Ml + 2w, N): [w rows of the lower neighbour | x | w rows of the upper
+    neighbour]; zeros where the global sequence ends."""
+    B, Ml, N = x.shape
+    if Ml < window:
+        raise RuntimeError("sequence shard of %d rows is shorter than the window %d" % (Ml, window))
+    _, _, lo, hi = _neighbours(group)
+    ext = x.new_zeros((B, Ml + 2 * window, N))
+    ext[:, window:window + Ml] = x
+    ops, keep = [], []
+    if lo is not None:
+        head = x[:, :window].contiguous()
+        recv_lo = x.new_empty((B, window, N))
+        keep += [head, recv_lo]
+        ops += [dist.P2POp(dist.isend, head, lo, group), dist.P2POp(dist.irecv, recv_lo, lo, group)]
+    if hi is not None:
+        tail = x[:, Ml - window:].contiguous()
+        recv_hi = x.new_empty((B, window, N))
+        keep += [tail, recv_hi]
+        ops += [dist.P2POp(dist.isend, tail, hi, group), dist.P2POp(dist.irecv, recv_hi, hi, group)]
+    if ops:
+        for req in dist.batch_isend_irecv(ops):
+            req.wait()
+    if lo is not None:
+        ext[:, :window] = recv_lo
+    if hi is not None:
+        ext[:, window + Ml:] = recv_hi
+    return ext
+
+
+def reduce_halo(part: torch.Tensor, window: int, group=None) -> torch.Tensor:
+    """part (B, Ml + 2w, N): this rank's contributions to positions [m0 - w, m0 + Ml + w).  Sends the two
+    halo strips to the neighbours that own those positions and adds what they send: -> (B, Ml, N)."""
+    B, Mext, N = part.shape
+    Ml = Mext - 2 * window
+    _, _, lo, hi = _neighbours(group)
+    own = part[:, window:window + Ml].clone()
+    ops, bufs = [], {}
+    if lo is not None:
+        send = part[:, :window].contiguous()
+        bufs["lo"] = part.new_empty((B, window, N))
+        bufs["lo_send"] = send
+        ops += [dist.P2POp(dist.isend, send, lo, group), dist.P2POp(dist.irecv, bufs["lo"], lo, group)]
+    if hi is not None:
+        send = part[:, window + Ml:].contiguous()
+        bufs["hi"] = part.new_empty((B, window, N))
+        bufs["hi_send"] = send
+        ops += [dist.P2POp(dist.isend, send, hi, group), dist.P2POp(dist.irecv, bufs["hi"], hi, group)]
+    if ops:
+        for req in dist.batch_isend_irecv(ops):
+            req.wait()
+    if lo is not None:
+        own[:, :window] += bufs["lo"]
+    if hi is not None:
+        own[:, Ml - window:] += bufs["hi"]
+    return own
+
+
+def _local_seq(Ml: int, window: int, group) -> Tuple[int, int]:
+    """In-sequence range of the extended row space [m0 - w, m0 + Ml + w) of this rank."""
+    rank, world, _, _ = _neighbours(group)
+    return (window if rank == 0 else 0, Ml + window if rank == world - 1 else Ml + 2 * window)
+
+
+class _SeqWindowMatmul(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, kt, window, group):
+        kt_ext = exchange_halo(kt, window, group)
+        seq = _local_seq(q.shape[1], window, group)
+        a = primitives.band_nt(q, kt_ext, window, other_off=window, seq=seq)
+        ctx.save_for_backward(q, kt_ext)
+        ctx.window, ctx.group, ctx.seq = window, group, seq
+        return a
+
+    @staticmethod
+    def backward(ctx, grad_a):
+        q, kt_ext = ctx.saved_tensors
+        w, seq = ctx.window, ctx.seq
+        grad_a = grad_a.contiguous()
+        gq = primitives.band_n(grad_a, kt_ext, w, other_off=w, seq=seq)
+        part = primitives.band_t(grad_a, q, w, other_rows=kt_ext.shape[1], other_off=w, seq=seq)
+        gkt = reduce_halo(part, w, ctx.group)
+        return gq, gkt, None, None
+
+
+class _SeqUnwindowMatmul(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a, v, window, group):
+        v_ext = exchange_halo(v, window, group)
+        seq = _local_seq(v.shape[1], window, group)
+        a = a.contiguous()
+        o = primitives.band_n(a, v_ext, window, other_off=window, seq=seq)
+        ctx.save_for_backward(a, v_ext)
+        ctx.window, ctx.group, ctx.seq = window, group, seq
+        return o
+
+    @staticmethod
+    def backward(ctx, grad_o):
+        a, v_ext = ctx.saved_tensors
+        w, seq = ctx.window, ctx.seq
+        grad_o = grad_o.contiguous()
+        ga = primitives.band_nt(grad_o, v_ext, w, other_off=w, seq=seq)
+        part = primitives.band_t(a, grad_o, w, other_rows=v_ext.shape[1], other_off=w, seq=seq)
+        gv = reduce_halo(part, w, ctx.group)
+        return ga, gv, None, None
+
+
+def seq_parallel_window_matmul(inp: torch.Tensor, other: torch.Tensor, window_size: int, group=None) -> torch.Tensor:
+    """`window_matmul` on a sequence shard.  inp (*, Ml, N), other (*, N, Ml): this rank's rows of Q and
+    columns of K.  Returns this rank's rows of the band, (*, Ml, 2w+1)."""
+    if not window_size:
+        return (inp * other.transpose(-1, -2)).sum(dim=-1, keepdim=True)
+    *dims, seq_len, hidden = inp.shape
+    q = inp.reshape(-1, seq_len, hidden)
+    kt = other.reshape(-1, hidden, seq_len).transpose(-1, -2)
+    out = _SeqWindowMatmul.apply(q, kt, window_size, group)
+    return out.reshape(*dims, seq_len, 2 * window_size + 1)
+
+
+def seq_parallel_unwindow_matmul(inp: torch.Tensor, other: torch.Tensor, window_size: int, group=None) -> torch.Tensor:
+    """`unwindow_matmul` on a sequence shard.  inp (*, Ml, 2w+1), other (*, Ml, N) -> (*, Ml, N)."""
+    if not window_size:
+        return inp * other
+    *dims, seq_len, hidden = other.shape
+    a = inp.reshape(-1, seq_len, 2 * window_size + 1)
+    v = other.reshape(-1, seq_len, hidden)
+    out = _SeqUnwindowMatmul.apply(a, v, window_size, group)
+    return out.reshape(*dims, seq_len, hidden)
+
+
+def shard_batch(t: torch.Tensor, group=None) -> torch.Tensor:
+    """This rank's slice of the flattened batch dimension (dim 0), in contiguous blocks of ceil(B / P)."""
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    per = (t.shape[0] + world - 1) // world
+    return t[rank * per:(rank + 1) * per]

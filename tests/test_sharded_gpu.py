@@ -1,0 +1,78 @@
+"""Sequence-sharded operators on real GPUs over NCCL (needs >= 2 GPUs; skipped otherwise).
+
+Child processes, one per GPU; ranks only ever leave between steps.  NVLS is switched off and the kernels use
+no peer memory: the exchange is NCCL send/recv between neighbours."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, shape, dtype_name, out_dir):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    sys.path[:0] = [ROOT, os.path.join(ROOT, "pytorch-window-matmul_b200")]
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from window_matmul import _native, sharded
+
+        dtype = getattr(torch, dtype_name)
+        B, M, N, w = shape
+        g = torch.Generator().manual_seed(5)
+        q, k, v = (torch.randn(B, M, N, generator=g) / N ** 0.5 for _ in range(3))
+        go = torch.randn(B, M, N, generator=g)
+        Ml = M // world
+        sl = slice(rank * Ml, (rank + 1) * Ml)
+        ql, kl, vl = (t[:, sl].to(dtype).to(dev).requires_grad_(True) for t in (q, k, v))
+        a = sharded.seq_parallel_window_matmul(ql, kl.transpose(-1, -2), w)
+        a.retain_grad()
+        o = sharded.seq_parallel_unwindow_matmul(a, vl, w)
+        o.backward(go[:, sl].to(dtype).to(dev))
+        torch.cuda.synchronize()
+        assert _native.device_status() == 0
+        np.savez(os.path.join(out_dir, "rank%d.npz" % rank), **{
+            key: t.detach().float().cpu().numpy()
+            for key, t in dict(a=a, o=o, gq=ql.grad, gk=kl.grad, gv=vl.grad, ga=a.grad).items()})
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("dtype_name,shape", [("float32", (2, 256, 16, 24)), ("bfloat16", (2, 1024, 64, 64)),
+                                              ("bfloat16", (1, 2048, 128, 256))])
+def test_sequence_sharded_on_gpus(tmp_path, dtype_name, shape):
+    import torch.multiprocessing as mp
+
+    import helpers as H
+
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least 2 GPUs")
+    mp.spawn(_worker, args=(world, _free_port(), shape, dtype_name, str(tmp_path)), nprocs=world, join=True)
+    B, M, N, w = shape
+    dtype = getattr(torch, dtype_name)
+    g = torch.Generator().manual_seed(5)
+    q, k, v = (H.round_to((torch.randn(B, M, N, generator=g) / N ** 0.5).numpy(), dtype) for _ in range(3))
+    go = H.round_to(torch.randn(B, M, N, generator=g).numpy(), dtype)
+    a, o, gq, gk, ga, gv = H.oracle.chain_fwd_bwd(q, np.ascontiguousarray(k.transpose(0, 2, 1)), v, w, go)
+    parts = [np.load(os.path.join(str(tmp_path), "rank%d.npz" % r)) for r in range(world)]
+    cat = lambda key: torch.from_numpy(np.concatenate([p[key] for p in parts], axis=1))  # noqa: E731
+    rel = 2e-5 if dtype == torch.float32 else 4e-2  # bf16: the band itself is rounded before it is reused
+    for key, want in dict(a=a, o=o, ga=ga, gq=gq, gk=gk.transpose(0, 2, 1), gv=gv).items():
+        H.assert_lowp_close(cat(key), want, key, rel=rel if key != "a" else min(rel, 1e-2))
