@@ -38,6 +38,9 @@ WORKLOADS = {
     "c5": (64, 16384, 64, 384, "bf16", "normal"),
 }
 METRIC = "fwd+bwd window+unwindow us at B=96 M=4096 N=64 w=256"
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch, per band row, from the ncu capture summarised in
+# profiles/band_kernels_c2_b48_bf16.md (B=48: 196608 rows per launch).
+NCU_DRAM_BYTES_PER_ROW = {"c2": {"band_nt": 1009.5, "band_n+band_t": 1484.1, "band_n": 1245.6, "band_t": 1226.1}}
 
 
 def algorithmic(B, M, N, w, e):
@@ -385,12 +388,10 @@ def run_ours(args, torch):
         total_bytes, total_flops = algorithmic(B, M, N, w, e)
         dom = max(per_kernel.items(), key=lambda kv: kv[1]["us"]) if per_kernel else (None, None)
         traffic = None
-        tpath = os.path.join(ROOT, "profiles", "ncu_traffic.json")
-        if dom[0] and os.path.exists(tpath):
-            with open(tpath) as f:
-                rec = json.load(f).get(args.workload, {}).get(dom[0].split()[-1])
-            if rec:  # bytes per band row, scaled to this rank's launch (traffic grows in proportion to rows)
-                traffic = rec["dram_bytes_per_row"] * Bl * M
+        if dom[0] and args.workload in NCU_DRAM_BYTES_PER_ROW:
+            per_row = NCU_DRAM_BYTES_PER_ROW[args.workload].get(dom[0].split()[-1])
+            if per_row:  # captured at B=48; traffic grows in proportion to the band rows of a launch
+                traffic = per_row * Bl * M
         line = {
             "metric": METRIC if args.workload == "c2" and not args.batch else "fwd+bwd window+unwindow us (%s)" % args.workload,
             "value": us_per_step, "unit": "us", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
