@@ -8,7 +8,8 @@
 // the box as a K-major A operand (rows = M, x = K); band_t uses the same bytes as an MN-major A operand
 // (x = M, rows = K).  Box elements that are not band entries of their row (they alias neighbouring rows)
 // or whose position is outside the sequence are zeroed in shared memory by the mask warps before the MMA
-// reads them; only the first and last chunk of a tile, and tiles at the sequence ends, need that.
+// reads them; only the first and last chunk of a tile, and tiles at the sequence ends, need that, and only
+// for those chunks does the MMA thread wait for the mask warps.
 //
 // MODE 0 = band_n, 1 = band_t, 2 = both over the SAME band in one launch (the backward of window_matmul:
 // grad_Q = band_n(grad_A, K^T), grad_K^T = band_t(grad_A, Q)).  In mode 2 the work items alternate
@@ -110,6 +111,19 @@ band_mm_tc_kernel(const __grid_constant__ CUtensorMap map_band, const __grid_con
     return t0 >= p.lo && t0 + 128 <= p.hi;
   };
 
+  // The MMA thread waits for the mask warps only at SYNC POINTS: every chunk that needs zeroing, and any
+  // chunk that would otherwise be the STAGES-th in a row without one.  Both sides evaluate this rule on the
+  // same chunk sequence.  Between two sync points fewer than STAGES chunks pass, so the producer can never
+  // refill a stage twice while a mask thread is still waiting for its earlier phase.
+  auto mask_sync = [&](bool plain, int &since) -> bool {
+    if (!plain || since >= S::STAGES - 1) {
+      since = 0;
+      return true;
+    }
+    ++since;
+    return false;
+  };
+
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
@@ -149,21 +163,25 @@ band_mm_tc_kernel(const __grid_constant__ CUtensorMap map_band, const __grid_con
       constexpr uint64_t ADESC_T = smem_desc_base(BT::BOX_BYTES, 1024, 2u);
       // B operand, MN-major: OT::BOXK contiguous hidden columns per row, next box one leading offset away.
       constexpr uint64_t BDESC = smem_desc_base(OT::BOX_BYTES, 8 * OT::SW_BYTES, OT::SWZ_CODE);
-      int it = 0, tit = 0;
+      int it = 0, tit = 0, since = 0, mk[S::STAGES];
+      for (int s = 0; s < S::STAGES; s++) mk[s] = 0;
       bool ok = true;
       for (int wi = blockIdx.x; ok && wi < total_items; wi += gridDim.x, ++tit) {
         const bool tr = item_tr(wi);
+        const int t0 = (item_tile(wi) % p.tiles_per_batch) * TILE;
         const uint32_t idesc = tr ? IDESC_T : IDESC_N;
         const uint64_t adesc = tr ? ADESC_T : ADESC_N;
         const int as = tit & 1;
         if (!(ok = mbar_wait(bar_acc_empty(as), ((tit >> 1) & 1) ^ 1, abort_flag))) break;
         for (int c = 0; c < p.nchunks; ++c, ++it) {
           const int s = it % S::STAGES;
-          // full: the TMA bytes have landed; masked: the mask warps are done with this stage.  The mask
-          // warps arrive for EVERY chunk (also those they do not touch) so that no role ever runs more
-          // than one barrier phase ahead of another, which parity waits cannot tell apart.
+          // full: the TMA bytes have landed.  masked: the mask warps are done with this stage; waited for
+          // only at sync points (see mask_sync below), i.e. for the chunks they had to touch.
           if (!(ok = mbar_wait(bar_full(s), (it / S::STAGES) & 1, abort_flag))) break;
-          if (!(ok = mbar_wait(bar_masked(s), (it / S::STAGES) & 1, abort_flag))) break;
+          if (mask_sync(chunk_is_plain(tr, t0, c), since)) {
+            if (!(ok = mbar_wait(bar_masked(s), mk[s] & 1, abort_flag))) break;
+            ++mk[s];
+          }
           tc_fence_after_sync();
           const uint32_t a_addr = base + s * S::STAGE_BYTES, b_addr = a_addr + BT::BYTES;
 #pragma unroll
@@ -181,7 +199,7 @@ band_mm_tc_kernel(const __grid_constant__ CUtensorMap map_band, const __grid_con
   } else if (warp < 6) {
     // ---------------- mask warps: thread <-> row of the band box ----------------
     const int row = (warp - 2) * 32 + lane;
-    int it = 0;
+    int it = 0, since = 0;
     bool ok = true;
     for (int wi = blockIdx.x; ok && wi < total_items; wi += gridDim.x) {
       const int tile = item_tile(wi);
@@ -189,9 +207,12 @@ band_mm_tc_kernel(const __grid_constant__ CUtensorMap map_band, const __grid_con
       const int t0 = (tile % p.tiles_per_batch) * TILE;
       for (int c = 0; c < p.nchunks; ++c, ++it) {
         const int s = it % S::STAGES;
+        // every phase of every stage is observed (a parity wait cannot tell phases two apart)
         if (!(ok = mbar_wait(bar_full(s), (it / S::STAGES) & 1, abort_flag))) break;
-        if (chunk_is_plain(tr, t0, c)) {
-          mbar_arrive(bar_masked(s));
+        const bool plain = chunk_is_plain(tr, t0, c);
+        const bool sync = mask_sync(plain, since);
+        if (plain) {
+          if (sync) mbar_arrive(bar_masked(s));
           continue;
         }
         // columns [col_lo, col_hi] of this row are band entries inside the sequence; the rest is zeroed
@@ -205,21 +226,36 @@ band_mm_tc_kernel(const __grid_constant__ CUtensorMap map_band, const __grid_con
           col_hi = min(row + c * 128, p.hi - t0 - 1);
         }
         const uint32_t tile_addr = base + s * S::STAGE_BYTES;
-#pragma unroll
-        for (int g = 0; g < 16; g++) {
+        // 16-byte piece g (8 columns) of this row: box g / 8, swizzled column (g % 8) ^ (row % 8)
+        auto piece = [&](int g) -> uint32_t {
+          return tile_addr + (g >> 3) * BT::BOX_BYTES + row * 128 + (((g & 7) ^ (row & 7)) << 4);
+        };
+        auto zero_piece = [&](int g) {
+          asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(piece(g)), "r"(0u) : "memory");
+        };
+        // keep columns [col_lo, col_hi] of piece g, zero its other columns
+        auto trim_piece = [&](int g) {
+          const uint32_t a = piece(g);
           const int c0 = g * 8;
-          if (c0 >= col_lo && c0 + 7 <= col_hi) continue;
-          const uint32_t a = tile_addr + (g >> 3) * BT::BOX_BYTES + row * 128 + (((g & 7) ^ (row & 7)) << 4);
-          uint32_t v0 = 0, v1 = 0, v2 = 0, v3 = 0;
-          if (c0 + 7 >= col_lo && c0 <= col_hi) {
-            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3) : "r"(a) : "memory");
-            auto keep = [&](int col) { return col >= col_lo && col <= col_hi; };
-            v0 &= (keep(c0 + 0) ? 0x0000ffffu : 0u) | (keep(c0 + 1) ? 0xffff0000u : 0u);
-            v1 &= (keep(c0 + 2) ? 0x0000ffffu : 0u) | (keep(c0 + 3) ? 0xffff0000u : 0u);
-            v2 &= (keep(c0 + 4) ? 0x0000ffffu : 0u) | (keep(c0 + 5) ? 0xffff0000u : 0u);
-            v3 &= (keep(c0 + 6) ? 0x0000ffffu : 0u) | (keep(c0 + 7) ? 0xffff0000u : 0u);
+          uint32_t v[4];
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]) : "r"(a) : "memory");
+#pragma unroll
+          for (int k = 0; k < 4; k++) {
+            const int ca = c0 + 2 * k, cb = ca + 1;
+            v[k] &= ((ca >= col_lo && ca <= col_hi) ? 0x0000ffffu : 0u) | ((cb >= col_lo && cb <= col_hi) ? 0xffff0000u : 0u);
           }
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(v0), "r"(v1), "r"(v2), "r"(v3) : "memory");
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]) : "memory");
+        };
+        if (col_lo > col_hi || col_hi < 0 || col_lo > 127) {
+#pragma unroll 4
+          for (int g = 0; g < 16; g++) zero_piece(g);
+        } else {
+          const int lo = max(col_lo, 0), hi = min(col_hi, 127);
+          const int g_lo = lo >> 3, g_hi = hi >> 3;  // first / last piece with a column to keep
+          for (int g = 0; g < g_lo; g++) zero_piece(g);
+          for (int g = g_hi + 1; g < 16; g++) zero_piece(g);
+          if ((lo & 7) != 0 || (g_lo == g_hi && (hi & 7) != 7)) trim_piece(g_lo);
+          if (g_hi != g_lo && (hi & 7) != 7) trim_piece(g_hi);
         }
         if (!tr) {
           // rows of the other operand whose position is outside the sequence: zero them too, so that

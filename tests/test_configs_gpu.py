@@ -1,0 +1,153 @@
+"""The benchmark configurations at FULL size on one GPU: size-independent properties over the whole tensors
+and oracle parity on slices the CPU finishes in seconds.
+
+Config 1 (fp32, full chain, bit-exact) lives in test_parity_gpu.py::test_config1_chain_fp32; config 4's
+sequence sharding and config 5's batch sharding are covered by test_sharded*.py / bench.py --gpus N."""
+import importlib
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import helpers as H
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def wm():
+    from window_matmul import _native
+
+    impl = importlib.import_module("window_matmul.window_matmul")
+    yield impl
+    assert _native.device_status() == 0
+
+
+def _seeded(B, M, N, dtype, seed, dist="normal_scaled"):
+    g = torch.Generator().manual_seed(seed)
+    if dist == "uniform":
+        mk = lambda: torch.rand(B, M, N, generator=g)  # noqa: E731
+    else:
+        s = 1.0 / math.sqrt(N) if dist == "normal_scaled" else 1.0
+        mk = lambda: torch.randn(B, M, N, generator=g) * s  # noqa: E731
+    return [mk().to(dtype) for _ in range(4)]  # q, k^T, v, upstream grad
+
+
+def _oracle_rows(q, kt, v, w, rows):
+    """Oracle on the first `rows` rows of one sequence: those rows only see positions < rows + w, so the
+    truncated sequence of rows + w positions gives the same values."""
+    n = rows + w
+    q, kt, v = (t[:, :n].float().numpy() for t in (q, kt, v))
+    a = H.oracle.window_matmul_forward(q, np.ascontiguousarray(kt.transpose(0, 2, 1)), w)
+    return a[:, :rows]
+
+
+def _chain(wm, q, kt, v, go, w):
+    import window_matmul as pkg
+
+    qd, ktd, vd = (t.cuda().requires_grad_(True) for t in (q, kt, v))
+    a = pkg.window_matmul(qd, ktd.transpose(-1, -2), w)
+    a.retain_grad()
+    o = pkg.unwindow_matmul(a, vd, w)
+    o.backward(go.cuda())
+    torch.cuda.synchronize()
+    return dict(a=a.detach(), o=o.detach(), gq=qd.grad, gk=ktd.grad, gv=vd.grad, ga=a.grad)
+
+
+def _check_properties(wm, got, q, kt, w, M):
+    """Size-independent checks on the whole tensors."""
+    from window_matmul import _native as N
+
+    mask = torch.from_numpy(H.out_of_sequence_mask(M, w)).cuda()
+    assert (got["a"][:, mask] == 0).all() and (got["ga"][:, mask] == 0).all()
+    for t in got.values():
+        assert torch.isfinite(t).all()
+    # exact homogeneity: scaling Q by 2 scales the band by exactly 2 (a power of two commutes with rounding)
+    a2 = wm.band_nt((q * 2).cuda(), kt.cuda(), w)
+    assert torch.equal(a2, got["a"] * 2)
+    # batch entries are independent: reversing the batch reverses the result bit for bit
+    ar = wm.band_nt(q.flip(0).cuda(), kt.flip(0).cuda(), w)
+    assert torch.equal(ar, got["a"].flip(0))
+    # the tensor-core path really ran where it should
+    if q.dtype != torch.float32:
+        assert N.lib.wmm_query_path(N.BAND_NT, N.operand(q.cuda()), N.operand(kt.cuda()), got["a"].data_ptr(),
+                                    N.geometry(q.shape[0], M, q.shape[2], w), N.dtype_code(q), 0) == 1
+
+
+def test_config2_full_size_bf16(wm):
+    B, M, Nn, w = 96, 4096, 64, 256
+    q, kt, v, go = _seeded(B, M, Nn, torch.bfloat16, 0)
+    got = _chain(wm, q, kt, v, go, w)
+    _check_properties(wm, got, q, kt, w, M)
+    # oracle parity of all six results on the first and the last batch entry
+    for b in (0, B - 1):
+        sl = slice(b, b + 1)
+        d = dict(q=q[sl].float().numpy(), kt=kt[sl].float().numpy(), v=v[sl].float().numpy())
+        a, o, gq, gk, ga, gv = H.oracle.chain_fwd_bwd(d["q"], np.ascontiguousarray(d["kt"].transpose(0, 2, 1)), d["v"], w,
+                                                      go[sl].float().numpy())
+        H.assert_lowp_close(got["a"][sl], a, "a")
+        # downstream of A the kernels consume the bf16-rounded band, the oracle the fp32 one
+        for key, want in dict(o=o, ga=ga, gq=gq, gk=gk.transpose(0, 2, 1), gv=gv).items():
+            H.assert_lowp_close(got[key][sl], want, key, rel=4e-2)
+
+
+def test_config3_full_size_fp16_small_window(wm):
+    B, M, Nn, w = 1024, 2048, 32, 8
+    q, kt, v, go = _seeded(B, M, Nn, torch.float16, 1, dist="uniform")
+    got = _chain(wm, q, kt, v, go, w)
+    _check_properties(wm, got, q, kt, w, M)
+    sl = slice(0, 4)
+    a, o, gq, gk, ga, gv = H.oracle.chain_fwd_bwd(q[sl].float().numpy(), np.ascontiguousarray(kt[sl].float().numpy().transpose(0, 2, 1)),
+                                                  v[sl].float().numpy(), w, go[sl].float().numpy())
+    H.assert_lowp_close(got["a"][sl], a, "a")
+    for key, want in dict(o=o, ga=ga, gq=gq, gk=gk.transpose(0, 2, 1), gv=gv).items():
+        H.assert_lowp_close(got[key][sl], want, key, rel=4e-2)
+
+
+def test_config4_long_sequence_bf16(wm):
+    """B=16, M=65536, N=128, w=512 on ONE GPU (the sharded form is tested in test_sharded_gpu.py)."""
+    B, M, Nn, w = 16, 65536, 128, 512
+    q, kt, v, go = _seeded(B, M, Nn, torch.bfloat16, 4)
+    a = wm.band_nt(q.cuda(), kt.cuda(), w)
+    torch.cuda.synchronize()
+    mask = torch.from_numpy(H.out_of_sequence_mask(M, w)).cuda()
+    assert (a[:, mask] == 0).all() and torch.isfinite(a).all()
+    rows = 1024
+    want = _oracle_rows(q[:1], kt[:1], v[:1], w, rows)
+    H.assert_lowp_close(a[:1, :rows], want, "a, first rows")
+    # the rest of the chain against the exact-order CUDA-core kernels on one batch entry
+    from window_matmul import _native as N
+
+    vd, gd, ad = v[:1].cuda(), go[:1].cuda(), a[:1].contiguous()
+    o = wm.band_n(ad, vd, w)
+    gv = wm.band_t(ad, gd, w)
+    o_ref = wm.band_n(ad.float(), vd.float(), w, flags=N.FLAG_FORCE_GENERIC)
+    gv_ref = wm.band_t(ad.float(), gd.float(), w, flags=N.FLAG_FORCE_GENERIC)
+    H.assert_lowp_close(o, o_ref.cpu().numpy(), "o")
+    H.assert_lowp_close(gv, gv_ref.cpu().numpy(), "gv")
+
+
+def test_config5_attention_block_bf16_vs_fp32(wm):
+    """a = window_matmul(q,k,w)/sqrt(N); softmax with out-of-sequence slots at -inf; o = unwindow_matmul(p,v,w);
+    backward.  bf16 through the tensor-core kernels against fp32 through the exact-order kernels, at the
+    config's M, N, w and a reduced batch."""
+    import window_matmul as pkg
+
+    B, M, Nn, w = 4, 16384, 64, 384
+    q, kt, v, go = _seeded(B, M, Nn, torch.float32, 5, dist="normal")
+    mask = torch.from_numpy(H.out_of_sequence_mask(M, w)).cuda()
+
+    def block(dtype):
+        qd, ktd, vd = (t.to(dtype).cuda().requires_grad_(True) for t in (q, kt, v))
+        s = pkg.window_matmul(qd, ktd.transpose(-1, -2), w) / math.sqrt(Nn)
+        s = s.masked_fill(mask, float("-inf"))
+        p = torch.softmax(s.float(), dim=-1).to(dtype)
+        o = pkg.unwindow_matmul(p, vd, w)
+        o.backward(go.to(dtype).cuda())
+        return [t.detach().float() for t in (o, qd.grad, ktd.grad, vd.grad)]
+
+    lo = block(torch.bfloat16)
+    ref = block(torch.float32)
+    for name, x, y in zip(("o", "gq", "gk", "gv"), lo, ref):
+        H.assert_lowp_close(x, y.cpu().numpy(), name, rel=5e-2)
