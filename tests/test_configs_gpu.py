@@ -130,24 +130,51 @@ def test_config4_long_sequence_bf16(wm):
 
 def test_config5_attention_block_bf16_vs_fp32(wm):
     """a = window_matmul(q,k,w)/sqrt(N); softmax with out-of-sequence slots at -inf; o = unwindow_matmul(p,v,w);
-    backward.  bf16 through the tensor-core kernels against fp32 through the exact-order kernels, at the
-    config's M, N, w and a reduced batch."""
+    backward.  At the config's M, N, w and a reduced batch.  Every one of the six contractions of the bf16
+    block is compared at 1e-2 with the exact-order fp32 kernels on the SAME (bf16-valued) inputs; the whole
+    block is then compared with an all-fp32 block at a looser bound, because bf16 rounding of the
+    probabilities and of the N(0,1)-scale scores compounds through the softmax."""
     import window_matmul as pkg
+    from window_matmul import _native as N
 
     B, M, Nn, w = 4, 16384, 64, 384
     q, kt, v, go = _seeded(B, M, Nn, torch.float32, 5, dist="normal")
     mask = torch.from_numpy(H.out_of_sequence_mask(M, w)).cuda()
+    G = N.FLAG_FORCE_GENERIC
 
+    # ---- per contraction, identical inputs ----
+    bf = torch.bfloat16
+    qb, ktb, vb, gob = (t.to(bf).cuda() for t in (q, kt, v, go))
+    kb = ktb.transpose(-1, -2)
+    a = wm.window_matmul_forward(qb, kb, w)
+    H.assert_lowp_close(a, wm.band_nt(qb.float(), ktb.float(), w, flags=G).cpu().numpy(), "a")
+    s = (a.float() / math.sqrt(Nn)).masked_fill(mask, float("-inf")).requires_grad_(True)
+    pf = torch.softmax(s, dim=-1)
+    p = pf.to(bf)
+    o = wm.unwindow_matmul_forward(p, vb, w)
+    H.assert_lowp_close(o, wm.band_n(p.float(), vb.float(), w, flags=G).cpu().numpy(), "o")
+    gp, gv = wm.unwindow_matmul_backward(p, vb, w, gob)
+    H.assert_lowp_close(gp, wm.band_nt(gob.float(), vb.float(), w, flags=G).cpu().numpy(), "grad_p")
+    H.assert_lowp_close(gv, wm.band_t(p.float(), gob.float(), w, flags=G).cpu().numpy(), "grad_v")
+    (gs,) = torch.autograd.grad(pf, s, gp.float())
+    gs = (gs / math.sqrt(Nn)).to(bf)
+    assert (gs[:, mask] == 0).all()
+    gq, gk = wm.window_matmul_backward(qb, kb, w, gs)
+    H.assert_lowp_close(gq, wm.band_n(gs.float(), ktb.float(), w, flags=G).cpu().numpy(), "grad_q")
+    H.assert_lowp_close(gk.transpose(-1, -2), wm.band_t(gs.float(), qb.float(), w, flags=G).cpu().numpy(), "grad_k")
+    del a, s, pf, p, gp, gs
+
+    # ---- the whole block through the public API ----
     def block(dtype):
         qd, ktd, vd = (t.to(dtype).cuda().requires_grad_(True) for t in (q, kt, v))
-        s = pkg.window_matmul(qd, ktd.transpose(-1, -2), w) / math.sqrt(Nn)
-        s = s.masked_fill(mask, float("-inf"))
-        p = torch.softmax(s.float(), dim=-1).to(dtype)
-        o = pkg.unwindow_matmul(p, vd, w)
-        o.backward(go.to(dtype).cuda())
-        return [t.detach().float() for t in (o, qd.grad, ktd.grad, vd.grad)]
+        sc = pkg.window_matmul(qd, ktd.transpose(-1, -2), w) / math.sqrt(Nn)
+        sc = sc.masked_fill(mask, float("-inf"))
+        pr = torch.softmax(sc.float(), dim=-1).to(dtype)
+        out = pkg.unwindow_matmul(pr, vd, w)
+        out.backward(go.to(dtype).cuda())
+        return [t.detach().float() for t in (out, qd.grad, ktd.grad, vd.grad)]
 
     lo = block(torch.bfloat16)
     ref = block(torch.float32)
     for name, x, y in zip(("o", "gq", "gk", "gv"), lo, ref):
-        H.assert_lowp_close(x, y.cpu().numpy(), name, rel=5e-2)
+        H.assert_lowp_close(x, y.cpu().numpy(), name, rel=1e-1)
