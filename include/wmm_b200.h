@@ -75,7 +75,8 @@ enum {
   WMM_FLAG_SPLIT_ROUNDING = 1u << 0,
   /* never take a tensor-core kernel, whatever the shape (testing, and exact fp32 ordering). */
   WMM_FLAG_FORCE_GENERIC = 1u << 1,
-  /* fail with WMM_ERR_UNSUPPORTED instead of taking the generic kernel (testing the fast path). */
+  /* fail with WMM_ERR_UNSUPPORTED instead of taking the CUDA-core kernels (testing the fast paths:
+   * families 1 and 2 of wmm_query_path). */
   WMM_FLAG_REQUIRE_TENSOR = 1u << 2
 };
 
@@ -114,8 +115,8 @@ WMM_API uint64_t wmm_launch_count(void);
 /* Reads (and, if `clear` is non-zero, resets) the status word that a kernel sets when one of its bounded
  * waits runs out.  0 = clean.  Synchronises the current device.  Returns the word, or a negative status. */
 WMM_API int64_t wmm_device_status(int clear);
-/* Which kernel family the dispatcher picks for a problem: 0 = generic CUDA-core kernel, 1 = tcgen05
- * tensor-core kernel.  `primitive` is 1 (band_nt), 2 (band_n) or 3 (band_t); the operands carry the
+/* Which kernel family the dispatcher picks for a problem: 0 = exact-order CUDA-core kernels, 1 = tcgen05
+ * kernels, 2 = small-window kernels (w <= 32; warp-level MMAs fed from coalesced shared-memory tiles).  `primitive` is 1 (band_nt), 2 (band_n) or 3 (band_t); the operands carry the
  * strides and alignment that decide; pass the same arguments as to the compute call.  Negative = status. */
 WMM_API int wmm_query_path(int primitive, const wmm_operand *a, const wmm_operand *b, const void *band,
                    const wmm_geometry *g, int dtype, unsigned flags);

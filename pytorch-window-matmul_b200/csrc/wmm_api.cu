@@ -99,22 +99,28 @@ void set_band_o(wmm::Problem &p, void *band) {
   p.o_sb = p.o_sr = p.o_sc = 0;
 }
 
-bool wants_tensor(wmm::Primitive prim, const wmm::Problem &p) {
-  if (p.flags & (WMM_FLAG_FORCE_GENERIC | WMM_FLAG_SPLIT_ROUNDING)) return false;
-  return wmm::tensor_eligible(prim, p);
+// Kernel family for a problem: 0 = exact-order CUDA-core kernels, 1 = tcgen05 kernels, 2 = small-window kernels.
+int pick_family(wmm::Primitive prim, const wmm::Problem &p) {
+  if (p.flags & (WMM_FLAG_FORCE_GENERIC | WMM_FLAG_SPLIT_ROUNDING)) return 0;
+  if (wmm::small_eligible(prim, p)) return 2;
+  if (wmm::tensor_eligible(prim, p)) return 1;
+  return 0;
 }
 
+bool wants_tensor(wmm::Primitive prim, const wmm::Problem &p) { return pick_family(prim, p) == 1; }
+
 int dispatch(wmm::Primitive prim, const wmm::Problem &p, void *stream) {
-  const bool tensor = wants_tensor(prim, p);
-  if (!tensor && (p.flags & WMM_FLAG_REQUIRE_TENSOR))
+  const int family = pick_family(prim, p);
+  if (family == 0 && (p.flags & WMM_FLAG_REQUIRE_TENSOR))
     return fail(WMM_ERR_UNSUPPORTED, "no tensor-core kernel takes this problem (primitive %d)", (int)prim);
   int launches = 0;
-  cudaError_t e = tensor ? wmm::launch_tensor(prim, p, (cudaStream_t)stream, &launches)
-                         : wmm::launch_generic(prim, p, (cudaStream_t)stream, &launches);
+  cudaError_t e = family == 1   ? wmm::launch_tensor(prim, p, (cudaStream_t)stream, &launches)
+                  : family == 2 ? wmm::launch_small(prim, p, (cudaStream_t)stream, &launches)
+                                : wmm::launch_generic(prim, p, (cudaStream_t)stream, &launches);
   g_launches.fetch_add((uint64_t)launches, std::memory_order_relaxed);
   if (e != cudaSuccess)
     return fail(WMM_ERR_CUDA, "CUDA error launching primitive %d: %s [%s]", (int)prim, cudaGetErrorString(e),
-                tensor ? wmm::launch_detail() : "generic kernel launch");
+                family == 1 ? wmm::launch_detail() : family == 2 ? "small-window kernel launch" : "generic kernel launch");
   return WMM_OK;
 }
 
@@ -210,7 +216,7 @@ int wmm_query_path(int primitive, const wmm_operand *a, const wmm_operand *b, co
   }
   if (s < 0) return s;
   if (s == 1) return 0;
-  return wants_tensor((wmm::Primitive)primitive, p) ? 1 : 0;
+  return pick_family((wmm::Primitive)primitive, p);
 }
 
 int wmm_band_nt(const wmm_operand *x, const wmm_operand *y, void *band, const wmm_geometry *g, int dtype,

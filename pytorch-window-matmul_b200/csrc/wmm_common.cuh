@@ -40,6 +40,10 @@ cudaError_t launch_tensor(Primitive prim, const Problem &p, cudaStream_t stream,
 bool tensor_fused_pair_eligible(const Problem &pn, const Problem &pt);
 cudaError_t launch_tensor_fused_pair(const Problem &pn, const Problem &pt, cudaStream_t stream, int *launches);
 
+// Small-window family (w <= 32, 16-bit): warp-level MMAs fed from coalesced shared-memory tiles.
+bool small_eligible(Primitive prim, const Problem &p);
+cudaError_t launch_small(Primitive prim, const Problem &p, cudaStream_t stream, int *launches);
+
 // Launchers describe a failure (which step, which driver code) here; the API layer appends it to the
 // error string of the calling thread.
 void set_launch_detail(const char *fmt, ...);

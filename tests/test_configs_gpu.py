@@ -72,7 +72,7 @@ def _check_properties(wm, got, q, kt, w, M):
     # the tensor-core path really ran where it should
     if q.dtype != torch.float32:
         assert N.lib.wmm_query_path(N.BAND_NT, N.operand(q.cuda()), N.operand(kt.cuda()), got["a"].data_ptr(),
-                                    N.geometry(q.shape[0], M, q.shape[2], w), N.dtype_code(q), 0) == 1
+                                    N.geometry(q.shape[0], M, q.shape[2], w), N.dtype_code(q), 0) in (1, 2)
 
 
 def test_config2_full_size_bf16(wm):

@@ -26,6 +26,11 @@ SHAPES = [
 ]
 
 
+# small-window family (w <= 32): any window, ragged and odd sequence lengths, all three hidden sizes
+SMALL_SHAPES = [(2, 300, 32, 1), (3, 129, 64, 5), (2, 100, 128, 16), (1, 1, 32, 3), (2, 257, 64, 32), (5, 77, 32, 17),
+                (1, 2048, 32, 8)]
+
+
 @pytest.fixture(scope="module")
 def wm():
     from window_matmul import _native
@@ -159,13 +164,70 @@ def test_window_backward_fused_tensor(wm, shape):
     try:
         before = N.launch_count()
         gq, gk = wm.window_matmul_backward(q, kt.transpose(-1, -2), w, g_band)
-        assert N.launch_count() - before == 1
+        assert N.launch_count() - before == (1 if w > 32 else 2)  # one fused launch in the tcgen05 family
     finally:
         wm.set_flags(old)
     torch.cuda.synchronize()
     assert N.device_status() == 0
     H.assert_lowp_close(gq, want_gq, "grad_q %s" % (shape,))
     H.assert_lowp_close(gk, want_gk, "grad_k %s" % (shape,))
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", SMALL_SHAPES)
+def test_small_window_family(wm, shape, dtype):
+    from window_matmul import _native as N
+
+    B, M, Nn, w = shape
+    d = _inputs(shape, dtype, seed=13)
+    want = H.oracle_all(d, w)
+    q, kt, v, g_out, g_band = (H.to_dev(d[x], dtype) for x in ("q", "kt", "v", "g_out", "g_band"))
+    att = d["att"].copy()
+    att[:, H.out_of_sequence_mask(M, w)] = np.nan  # never read
+    att = H.to_dev(att, dtype)
+    geo = N.geometry(B, M, Nn, w)
+    assert N.lib.wmm_query_path(N.BAND_NT, N.operand(q), N.operand(kt), 256, geo, N.dtype_code(q), 0) == 2
+    F = N.FLAG_REQUIRE_TENSOR
+    a = torch.full((B, M, 2 * w + 1), float("nan"), dtype=dtype, device="cuda")
+    wm.band_nt(q, kt, w, out=a, flags=F)
+    o = wm.band_n(att, v, w, flags=F)
+    gv = wm.band_t(att, g_out, w, flags=F)
+    gq = wm.band_n(g_band, kt, w, flags=F)
+    gk = wm.band_t(g_band, q, w, flags=F)
+    gatt = wm.band_nt(g_out, v, w, flags=F)
+    torch.cuda.synchronize()
+    H.assert_lowp_close(a, want["a"], "a")
+    assert (a.float().cpu().numpy()[:, H.out_of_sequence_mask(M, w)] == 0).all()
+    H.assert_lowp_close(o, want["o"], "o")
+    H.assert_lowp_close(gv, want["gv"], "gv")
+    H.assert_lowp_close(gq, want["gq"], "gq")
+    H.assert_lowp_close(gk, want["gk"].transpose(0, 2, 1), "gk")
+    H.assert_lowp_close(gatt, want["gatt"], "gatt")
+
+
+def test_small_window_family_on_a_sequence_shard(wm):
+    from window_matmul import _native as N
+
+    B, M, Nn, w = 2, 192, 32, 8
+    dtype = torch.float16
+    d = _inputs((B, M, Nn, w), dtype, seed=17)
+    want = H.oracle_all(d, w)
+    parts, F = 3, N.FLAG_REQUIRE_TENSOR
+    Ml = M // parts
+    gv = np.zeros((B, M + 2 * w, Nn))
+    for r in range(parts):
+        m0 = r * Ml
+        seq = (max(0, w - m0), min(Ml + 2 * w, M - m0 + w))
+        pad = lambda x: np.pad(x, ((0, 0), (w, w), (0, 0)), constant_values=55.0)[:, m0:m0 + Ml + 2 * w]  # noqa: E731
+        att = H.to_dev(d["att"][:, m0:m0 + Ml], dtype)
+        a = wm.band_nt(H.to_dev(d["q"][:, m0:m0 + Ml], dtype), H.to_dev(pad(d["kt"]), dtype), w, other_off=w, seq=seq, flags=F)
+        H.assert_lowp_close(a, want["a"][:, m0:m0 + Ml], "a shard %d" % r)
+        o = wm.band_n(att, H.to_dev(pad(d["v"]), dtype), w, other_off=w, seq=seq, flags=F)
+        H.assert_lowp_close(o, want["o"][:, m0:m0 + Ml], "o shard %d" % r)
+        part = wm.band_t(att, H.to_dev(d["g_out"][:, m0:m0 + Ml], dtype), w, other_rows=Ml + 2 * w, other_off=w, seq=seq, flags=F)
+        assert (part[:, :seq[0]] == 0).all() and (part[:, seq[1]:] == 0).all()
+        gv[:, m0:m0 + Ml + 2 * w] += part.double().cpu().numpy()
+    H.assert_lowp_close(torch.from_numpy(gv[:, w:w + M]), want["gv"], "gv summed over shards")
 
 
 def test_ineligible_problems_are_reported_not_faked(wm):
