@@ -286,7 +286,25 @@ def run_ours(args, torch):
         if Bl > 0 and not args.no_graph:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
-                step()
+                if args.branches == 2:
+                    # The step is a small DAG, not a chain: window fwd feeds unwindow fwd and grad_V (both only
+                    # read A); grad_A needs only the upstream gradient and feeds the window backward.  Captured
+                    # with its real dependencies, the tail of one kernel (SMs running out of tiles) is filled
+                    # by another branch's kernel.
+                    s1, s2 = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+                    s1.wait_stream(stream)
+                    with torch.cuda.stream(s1):
+                        impl.band_nt(god, vd, w, out=ga)
+                        ops[3]()
+                    ops[0]()
+                    s2.wait_stream(stream)
+                    with torch.cuda.stream(s2):
+                        impl.band_t(a, god, w, out=gv)
+                    ops[1]()
+                    stream.wait_stream(s1)
+                    stream.wait_stream(s2)
+                else:
+                    step()
             for _ in range(2):
                 graph.replay()
             stream.synchronize()
@@ -400,7 +418,7 @@ def run_ours(args, torch):
             "config": {
                 "workload": workload_name(args.workload), "batch_per_gpu": per,
                 "l2": "no flush: one step touches %.0f MB per GPU, larger than the 126 MB L2" % (total_bytes / world / 1e6),
-                "launch": "cuda graph of %d kernels" % launches_per_step if graph is not None else "%d stream launches" % launches_per_step,
+                "launch": ("cuda graph of %d kernels, %s" % (launches_per_step, "dependency DAG" if args.branches == 2 else "one chain")) if graph is not None else "%d stream launches" % launches_per_step,
                 "k_layout": "transposed view of (B,M,N)",
             },
             "step_roofline": {
@@ -449,6 +467,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--branches", type=int, default=2, choices=[1, 2], help="capture the step as one chain (1) or with its real dependencies (2)")
     ap.add_argument("--no-graph", action="store_true", help="launch the six kernels on the stream instead of a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=0, help="override B of the workload (small cases for profiling)")
