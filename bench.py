@@ -364,16 +364,21 @@ def run_ours(args, torch):
         e2e_steps = max(3, min(args.steps, 20))
         outs_host = [torch.empty(Bl, M, N, dtype=dtype).pin_memory() for _ in range(4)]
 
+        from window_matmul.host_pipeline import batched_host_call
+
+        def chain(qh, kth, vh, goh):
+            """The four native calls of the reference's module (window_matmul_kernel.*: forward and backward of
+            both operators) on one device-resident chunk of the batch; results are freshly allocated."""
+            kh = kth.transpose(-1, -2)
+            att = impl.window_matmul_forward(qh, kh, w)
+            out = impl.unwindow_matmul_forward(att, vh, w)
+            g_att, g_v = impl.unwindow_matmul_backward(att, vh, w, goh)
+            g_q, g_k = impl.window_matmul_backward(qh, kh, w, g_att)
+            return out, g_q, g_k.transpose(-1, -2), g_v
+
         def e2e_step():
-            qh, kth, vh, goh = (t.to(dev, non_blocking=True) for t in host)
-            qh.requires_grad_(True)
-            kth.requires_grad_(True)
-            vh.requires_grad_(True)
-            att = pkg.window_matmul(qh, kth.transpose(-1, -2), w)
-            out = pkg.unwindow_matmul(att, vh, w)
-            out.backward(goh)
-            for dst, src in zip(outs_host, (out.detach(), qh.grad, kth.grad, vh.grad)):
-                dst.copy_(src, non_blocking=True)
+            # host tensors in, host tensors out; uploads, kernels and downloads of batch chunks overlap
+            batched_host_call(chain, host, chunks=args.e2e_chunks, device=dev, outputs=outs_host)
 
         run_e2e = Bl > 0 and not args.skip_e2e
         if run_e2e:
@@ -471,6 +476,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch the six kernels on the stream instead of a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=0, help="override B of the workload (small cases for profiling)")
+    ap.add_argument("--e2e-chunks", type=int, default=8, help="batch chunks of the host-buffer leg")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     args = ap.parse_args()
     import torch

@@ -431,3 +431,23 @@ def test_config1_chain_fp32(wm):
         mask = H.out_of_sequence_mask(M, w)
         assert (got["a"].cpu().numpy()[:, mask] == 0).all() and (got["ga"].cpu().numpy()[:, mask] == 0).all()
         assert abs(mask.mean() - 0.03149) < 1e-4  # 3.149 % of the band is out of sequence at this shape
+
+
+def test_host_pipeline_matches_direct_calls(wm):
+    """Host tensors streamed through the GPU in batch chunks give the same results as one device-resident call."""
+    from window_matmul.host_pipeline import batched_host_call
+
+    B, M, Nn, w = 10, 128, 64, 64
+    g = torch.Generator().manual_seed(3)
+    q, kt, v = (torch.randn(B, M, Nn, generator=g).to(torch.bfloat16).pin_memory() for _ in range(3))
+
+    def fn(qd, ktd, vd):
+        a = wm.window_matmul_forward(qd, ktd.transpose(-1, -2), w)
+        return a, wm.unwindow_matmul_forward(a, vd, w)
+
+    a_h, o_h = batched_host_call(fn, [q, kt, v], chunks=4)
+    a_d, o_d = fn(q.cuda(), kt.cuda(), v.cuda())
+    assert not a_h.is_cuda and a_h.shape == (B, M, 2 * w + 1)
+    assert torch.equal(a_h, a_d.cpu()) and torch.equal(o_h, o_d.cpu())
+    with pytest.raises(RuntimeError, match="host tensors"):
+        batched_host_call(fn, [q.cuda(), kt, v])
