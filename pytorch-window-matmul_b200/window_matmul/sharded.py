@@ -48,15 +48,34 @@ def _neighbours(group) -> Tuple[int, int, Optional[int], Optional[int]]:
     return rank, world, lo, hi
 
 
+_HALO_STORAGE = {}  # data_ptr of a local view -> (extended buffer, window); see alloc_with_halo
+
+
+def alloc_with_halo(batch: int, rows: int, cols: int, window: int, dtype, device):
+    """Storage for a sequence shard WITH room for its halos: returns (local, extended) where `extended` is a
+    (batch, rows + 2w, cols) buffer and `local` = extended[:, w:w+rows] is the view to keep the shard's rows in.
+    exchange_halo() on such a view fills the margins in place instead of copying the shard into a new buffer."""
+    ext = torch.zeros((batch, rows + 2 * window, cols), dtype=dtype, device=device)
+    local = ext[:, window:window + rows]
+    _HALO_STORAGE[local.data_ptr()] = (ext, window)
+    return local, ext
+
+
 def exchange_halo(x: torch.Tensor, window: int, group=None) -> torch.Tensor:
     """x (B, Ml, N) local rows -> (B, Ml + 2w, N): [w rows of the lower neighbour | x | w rows of the upper
-    neighbour]; zeros where the global sequence ends."""
+    neighbour]; zeros where the global sequence ends.  If x lives in storage from alloc_with_halo() only the
+    margins are written; otherwise x is copied into a new extended buffer."""
     B, Ml, N = x.shape
     if Ml < window:
         raise RuntimeError("sequence shard of %d rows is shorter than the window %d" % (Ml, window))
     _, _, lo, hi = _neighbours(group)
-    ext = x.new_zeros((B, Ml + 2 * window, N))
-    ext[:, window:window + Ml] = x
+    held = _HALO_STORAGE.get(x.data_ptr())
+    if held is not None and held[1] == window and held[0].shape == (B, Ml + 2 * window, N) and held[0].dtype == x.dtype \
+            and x.stride() == held[0][:, window:window + Ml].stride():
+        ext = held[0]
+    else:
+        ext = x.new_zeros((B, Ml + 2 * window, N))
+        ext[:, window:window + Ml] = x
     ops, keep = [], []
     if lo is not None:
         head = x[:, :window].contiguous()
@@ -80,11 +99,12 @@ def exchange_halo(x: torch.Tensor, window: int, group=None) -> torch.Tensor:
 
 def reduce_halo(part: torch.Tensor, window: int, group=None) -> torch.Tensor:
     """part (B, Ml + 2w, N): this rank's contributions to positions [m0 - w, m0 + Ml + w).  Sends the two
-    halo strips to the neighbours that own those positions and adds what they send: -> (B, Ml, N)."""
+    halo strips to the neighbours that own those positions and adds what they send, in place: returns the
+    (B, Ml, N) view part[:, w:w+Ml]."""
     B, Mext, N = part.shape
     Ml = Mext - 2 * window
     _, _, lo, hi = _neighbours(group)
-    own = part[:, window:window + Ml].clone()
+    own = part[:, window:window + Ml]
     ops, bufs = [], {}
     if lo is not None:
         send = part[:, :window].contiguous()
