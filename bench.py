@@ -40,7 +40,7 @@ WORKLOADS = {
 METRIC = "fwd+bwd window+unwindow us at B=96 M=4096 N=64 w=256"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, per band row, from the ncu capture summarised in
 # profiles/band_kernels_c2_b48_bf16.md (B=48: 196608 rows per launch).
-NCU_DRAM_BYTES_PER_ROW = {"c2": {"band_nt": 1009.5, "band_n+band_t": 1484.1, "band_n": 1245.6, "band_t": 1226.1}}
+NCU_DRAM_BYTES_PER_ROW = {"c2": {"band_nt": 1008.8, "band_n+band_t": 1474.3, "band_n": 1245.0, "band_t": 1242.9}}
 
 
 def algorithmic(B, M, N, w, e):
