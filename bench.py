@@ -209,6 +209,50 @@ def run_reference(args, torch):
     print(json.dumps(line), flush=True)
 
 
+def run_reference_cuda(args, torch):
+    """The reference's own CUDA kernels (csrc/window_matmul/cuda/window_matmul_cuda.cu, compiled unmodified by
+    oracle/build_ref.py) on this GPU, same workload, through its four pybind entry points.  The reference has
+    no bf16: bf16 workloads run in fp16 (same bytes).  Reported beside our numbers, not part of the contract's
+    two arms."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    ref_dir = os.path.join(ROOT, "oracle", "_ref")
+    if not os.path.exists(os.path.join(ref_dir, "WITH_CUDA")):
+        print(json.dumps({"impl": "reference_cuda", "unavailable": "oracle/_ref was built without the reference's CUDA sources"}))
+        return
+    sys.path.insert(0, ref_dir)
+    import window_matmul_kernel as ref
+
+    B, M, N, w, dt, dist = WORKLOADS[args.workload]
+    dtype = {"bf16": torch.float16, "fp16": torch.float16, "fp32": torch.float32}[dt]
+    e = 2 if dt != "fp32" else 4
+    q, kt, v, go = (t.to(dtype).cuda() for t in make_inputs(B, M, N, w, dist, 0, torch))
+    k = kt.transpose(-1, -2)  # a view: the reference's transposing copy (window_matmul_cuda.cu:236) is then free
+
+    def step():
+        a = ref.window_matmul_forward(q, k, w)
+        ref.unwindow_matmul_forward(a, v, w)
+        ga, _ = ref.unwindow_matmul_backward(a, v, w, go)
+        ref.window_matmul_backward(q, k, w, ga)
+
+    for _ in range(max(1, args.warmup)):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / args.steps
+    total_bytes, total_flops = algorithmic(B, M, N, w, e)
+    print(json.dumps({
+        "impl": "reference_cuda", "metric": "fwd+bwd window+unwindow us (%s)" % args.workload, "value": us, "unit": "us", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "dtype": "f16" if dt != "fp32" else "f32", "data": "synthetic",
+        "config": {"workload": workload_name(args.workload), "note": "reference CUDA kernels, legacy default stream, zero-filled outputs"},
+        "achieved_GBps": round(total_bytes / (us * 1e-6) / 1e9, 1), "TFLOPs": round(total_flops / (us * 1e-6) / 1e12, 2)}), flush=True)
+
+
 def workload_name(key):
     B, M, N, w, dt, dist = WORKLOADS[key]
     return "%s: B=%d M=%d N=%d w=%d %s fwd+bwd window_matmul->unwindow_matmul, %s inputs" % (key, B, M, N, w, dt, dist)
@@ -470,7 +514,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference_cuda"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--branches", type=int, default=2, choices=[1, 2], help="capture the step as one chain (1) or with its real dependencies (2)")
     ap.add_argument("--no-graph", action="store_true", help="launch the six kernels on the stream instead of a CUDA graph")
@@ -486,6 +530,8 @@ def main():
         WORKLOADS[args.workload] = (args.batch, M, N, w, dt, dist)
     if args.impl == "reference":
         run_reference(args, torch)
+    elif args.impl == "reference_cuda":
+        run_reference_cuda(args, torch)
     else:
         run_ours(args, torch)
 
