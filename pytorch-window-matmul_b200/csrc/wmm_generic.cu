@@ -8,8 +8,10 @@
 // the tensor-core kernels cannot take (hidden size 3, one-row sequences, odd windows, unaligned
 // pointers).
 //
-// All three primitives are the same register-tiled product C[64 x 64] += A[64 x 16] * B[16 x 64] in
-// dense coordinates (row, position); they differ only in how a dense coordinate maps to memory:
+// All three primitives are the same register-tiled product C[TM x TN] += A[TM x 16] * B[16 x TN] in
+// dense coordinates (row, position) -- fp32: 128 x 128 tiles (band_nt) or 128 x 64 (band_n, band_t), 8 x 8 or
+// 8 x 4 outputs per thread, next slice prefetched into registers -- and differ only in how a dense
+// coordinate maps to memory:
 //   band_nt  C(i, p) = sum_h X[i,h] Y[p,h]        stored at Band[i, p - off - i + w]
 //   band_n   C(i, h) = sum_p Band[i, p-off-i+w] Y[p,h]
 //   band_t   C(p, h) = sum_i Band[i, p-off-i+w] X[i,h]
@@ -21,9 +23,7 @@ namespace wmm {
 
 namespace {
 
-constexpr int TM = 64;   // output rows per CTA
-constexpr int TN = 64;   // output columns per CTA
-constexpr int TK = 16;   // reduction slice staged in shared memory
+constexpr int TK = 16;  // reduction slice staged in shared memory
 constexpr int PAD = 4;
 constexpr int THREADS = 256;
 
@@ -34,110 +34,156 @@ template <bool SPLIT> __device__ __forceinline__ double mac(double a, double b, 
   return SPLIT ? __dadd_rn(c, __dmul_rn(a, b)) : fma(a, b, c);
 }
 
-struct Tile {
-  int b, rt, ct;
+// Dense operand element (r, kidx) of a tile, r = output row (A operand) or output column (B operand),
+// kidx = reduction index counted from the first one the tile can need.  Every case is an affine address
+// plus a valid kidx range per r; outside the range the element is zero.
+template <typename T, int PRIM, bool IS_A> struct OperandView {
+  const T *base;          // element (r = 0, kidx = 0)
+  int64_t r_stride, k_stride;
+  int r_count;            // r < r_count exist
+  int lo0, hi0;           // kidx range common to all r
+  int w, W;
+  // band operands: the valid range also depends on r (the band is 2w+1 wide around the diagonal)
+  __device__ __forceinline__ void range(int r, int &lo, int &hi) const {
+    lo = lo0;
+    hi = hi0;
+    if (IS_A && PRIM != BAND_NT) {  // j = kidx - r (band_n) resp. r - kidx + 2w (band_t) must lie in [0, W)
+      lo = max(lo, r);
+      hi = min(hi, r + W);
+    }
+    if (r >= r_count) hi = lo;
+  }
+  __device__ __forceinline__ const T *at(int r, int kidx) const { return base + r * r_stride + kidx * k_stride; }
 };
 
-// A-operand fetch: dense element (m, k) of the tile, already converted to the accumulator type.
 template <typename T, int PRIM>
-__device__ __forceinline__ typename ElemTraits<T>::Acc fetch_a(const Problem &p, const Tile &t, int m, int kidx) {
-  using Acc = typename ElemTraits<T>::Acc;
+__device__ __forceinline__ void make_views(const Problem &p, int b, int rt, int ct, int TM, int TN, OperandView<T, PRIM, true> &A,
+                                           OperandView<T, PRIM, false> &B) {
   const int W = 2 * p.w + 1;
+  A.w = B.w = p.w;
+  A.W = B.W = W;
   if (PRIM == BAND_NT) {
-    const int i = t.rt * TM + m, h = kidx;
-    if (i >= p.M || h >= p.N) return Acc(0);
-    const T *x = static_cast<const T *>(p.a);
-    return ElemTraits<T>::load(x + t.b * p.a_sb + i * p.a_sr + h * p.a_sc);
+    const int i0 = rt * TM, p0 = rt * TM - p.w + p.off + ct * TN;
+    A.base = static_cast<const T *>(p.a) + b * p.a_sb + (int64_t)i0 * p.a_sr;
+    A.r_stride = p.a_sr; A.k_stride = p.a_sc; A.r_count = p.M - i0; A.lo0 = 0; A.hi0 = p.N;
+    B.base = static_cast<const T *>(p.b) + b * p.b_sb + (int64_t)p0 * p.b_sr;
+    B.r_stride = p.b_sr; B.k_stride = p.b_sc; A.w = p.w;
+    // column n <-> position p0 + n: valid iff in [lo, hi)
+    B.r_count = 0x7fffffff; B.lo0 = 0; B.hi0 = p.N;
+    (void)B;
   } else if (PRIM == BAND_N) {
-    // kidx counts positions from the first one any row of the tile can reach
-    const int i = t.rt * TM + m;
-    const int pos = t.rt * TM - p.w + p.off + kidx;
-    const int j = pos - p.off - i + p.w;
-    if (i >= p.M || j < 0 || j >= W || pos < p.lo || pos >= p.hi) return Acc(0);
-    const T *band = static_cast<const T *>(p.a);
-    return ElemTraits<T>::load(band + ((int64_t)t.b * p.M + i) * W + j);
+    const int i0 = rt * TM, c0 = ct * TN, pstart = i0 - p.w + p.off;  // kidx <-> position pstart + kidx
+    // band[(b*M + i0 + r) * W + (kidx - r)]
+    A.base = static_cast<const T *>(p.a) + ((int64_t)b * p.M + i0) * W;
+    A.r_stride = W - 1; A.k_stride = 1; A.r_count = p.M - i0; A.lo0 = p.lo - pstart; A.hi0 = p.hi - pstart;
+    B.base = static_cast<const T *>(p.b) + b * p.b_sb + (int64_t)pstart * p.b_sr + (int64_t)c0 * p.b_sc;
+    B.r_stride = p.b_sc; B.k_stride = p.b_sr; B.r_count = p.N - c0; B.lo0 = p.lo - pstart; B.hi0 = p.hi - pstart;
   } else {
-    const int pos = t.rt * TM + m;
-    const int i = t.rt * TM - p.off - p.w + kidx;
-    const int j = pos - p.off - i + p.w;
-    if (i < 0 || i >= p.M || j < 0 || j >= W || pos < p.lo || pos >= p.hi) return Acc(0);
-    const T *band = static_cast<const T *>(p.a);
-    return ElemTraits<T>::load(band + ((int64_t)t.b * p.M + i) * W + j);
-  }
-}
-
-// B-operand fetch: dense element (k, n).
-template <typename T, int PRIM>
-__device__ __forceinline__ typename ElemTraits<T>::Acc fetch_b(const Problem &p, const Tile &t, int kidx, int n) {
-  using Acc = typename ElemTraits<T>::Acc;
-  const T *y = static_cast<const T *>(p.b);
-  if (PRIM == BAND_NT) {
-    const int pos = t.rt * TM - p.w + p.off + t.ct * TN + n, h = kidx;
-    if (pos < p.lo || pos >= p.hi || h >= p.N) return Acc(0);
-    return ElemTraits<T>::load(y + t.b * p.b_sb + pos * p.b_sr + h * p.b_sc);
-  } else if (PRIM == BAND_N) {
-    const int pos = t.rt * TM - p.w + p.off + kidx, h = t.ct * TN + n;
-    if (pos < p.lo || pos >= p.hi || h >= p.N) return Acc(0);
-    return ElemTraits<T>::load(y + t.b * p.b_sb + pos * p.b_sr + h * p.b_sc);
-  } else {
-    const int i = t.rt * TM - p.off - p.w + kidx, h = t.ct * TN + n;
-    if (i < 0 || i >= p.M || h >= p.N) return Acc(0);
-    return ElemTraits<T>::load(y + t.b * p.b_sb + i * p.b_sr + h * p.b_sc);
+    const int p0 = rt * TM, c0 = ct * TN, istart = p0 - p.off - p.w;  // kidx <-> band row istart + kidx
+    // band[(b*M + istart + kidx) * W + (r - kidx + 2w)]
+    A.base = static_cast<const T *>(p.a) + ((int64_t)b * p.M + istart) * W + 2 * p.w;
+    A.r_stride = 1; A.k_stride = W - 1;
+    A.r_count = min(p.Mo, p.hi) - p0;  // positions beyond the sequence (or the output) produce zeros
+    A.lo0 = max(-istart, 0); A.hi0 = p.M - istart;
+    B.base = static_cast<const T *>(p.b) + b * p.b_sb + (int64_t)istart * p.b_sr + (int64_t)c0 * p.b_sc;
+    B.r_stride = p.b_sc; B.k_stride = p.b_sr; B.r_count = p.N - c0; B.lo0 = max(-istart, 0); B.hi0 = p.M - istart;
   }
 }
 
 // AKF / BKF: whether the reduction index is the fastest-varying one in memory for that operand, which
 // picks the thread-to-element mapping of the staging loads (coalescing only; results do not depend on it).
-template <typename T, int PRIM, bool SPLIT, bool AKF, bool BKF>
+template <typename T, int PRIM, bool SPLIT, bool AKF, bool BKF, int TM, int TN>
 __global__ void __launch_bounds__(THREADS) band_generic_kernel(const Problem p, int nrt, int nct, int klen) {
   using Acc = typename ElemTraits<T>::Acc;
+  constexpr int MR = TM / 16, MC = TN / 16;          // outputs per thread
+  constexpr int LA = TM * TK / THREADS, LB = TN * TK / THREADS;  // staged elements per thread and slice
   __shared__ Acc As[TK][TM + PAD];
   __shared__ Acc Bs[TK][TN + PAD];
 
-  Tile t;
+  int b, rt, ct;
   {
     int64_t lin = blockIdx.x;
-    t.ct = (int)(lin % nct);
+    ct = (int)(lin % nct);
     lin /= nct;
-    t.rt = (int)(lin % nrt);
-    t.b = (int)(lin / nrt);
+    rt = (int)(lin % nrt);
+    b = (int)(lin / nrt);
   }
   const int tid = threadIdx.x;
   const int ty = tid / 16, tx = tid % 16;
+  // Outputs of a thread: rows row_of(u), columns col_of(v).  Eight-wide micro-tiles are two groups of four,
+  // half a tile apart, so that the 16-byte shared-memory reads of neighbouring threads are contiguous.
+  auto row_of = [&](int u) -> int { return MR == 8 ? (u >> 2) * (TM / 2) + ty * 4 + (u & 3) : ty * MR + u; };
+  auto col_of = [&](int v) -> int { return MC == 8 ? (v >> 2) * (TN / 2) + tx * 4 + (v & 3) : tx * MC + v; };
 
-  Acc acc[4][4];
+  OperandView<T, PRIM, true> A;
+  OperandView<T, PRIM, false> B;
+  make_views<T, PRIM>(p, b, rt, ct, TM, TN, A, B);
+  // position bounds that depend on the output coordinate
+  const int pos0 = (PRIM == BAND_NT) ? rt * TM - p.w + p.off + ct * TN : rt * TM;  // band_nt: column 0; band_t: row 0
+
+  auto fetch_a = [&](int slot, int k0) -> Acc {
+    const int e = tid + slot * THREADS;
+    const int m = AKF ? e / TK : e % TM, k = AKF ? e % TK : e / TM;
+    int lo, hi;
+    A.range(m, lo, hi);
+    if (PRIM == BAND_T && pos0 + m < p.lo) hi = lo;
+    const int kidx = k0 + k;
+    return (kidx >= lo && kidx < hi) ? ElemTraits<T>::load(A.at(m, kidx)) : Acc(0);
+  };
+  auto fetch_b = [&](int slot, int k0) -> Acc {
+    const int e = tid + slot * THREADS;
+    const int n = BKF ? e / TK : e % TN, k = BKF ? e % TK : e / TN;
+    int lo, hi;
+    B.range(n, lo, hi);
+    if (PRIM == BAND_NT && (pos0 + n < p.lo || pos0 + n >= p.hi)) hi = lo;
+    const int kidx = k0 + k;
+    return (kidx >= lo && kidx < hi) ? ElemTraits<T>::load(B.at(n, kidx)) : Acc(0);
+  };
+
+  Acc acc[MR][MC];
 #pragma unroll
-  for (int u = 0; u < 4; u++)
+  for (int u = 0; u < MR; u++)
 #pragma unroll
-    for (int v = 0; v < 4; v++) acc[u][v] = Acc(0);
+    for (int v = 0; v < MC; v++) acc[u][v] = Acc(0);
+
+  Acc ra[LA], rb[LB];  // the next slice, prefetched while the current one is multiplied
+#pragma unroll
+  for (int s = 0; s < LA; s++) ra[s] = fetch_a(s, 0);
+#pragma unroll
+  for (int s = 0; s < LB; s++) rb[s] = fetch_b(s, 0);
 
   for (int k0 = 0; k0 < klen; k0 += TK) {
 #pragma unroll
-    for (int r = 0; r < (TM * TK) / THREADS; r++) {
-      const int e = tid + r * THREADS;
-      const int m = AKF ? e / TK : e % TM;
-      const int k = AKF ? e % TK : e / TM;
-      As[k][m] = (k0 + k < klen) ? fetch_a<T, PRIM>(p, t, m, k0 + k) : Acc(0);
+    for (int s = 0; s < LA; s++) {
+      const int e = tid + s * THREADS;
+      As[AKF ? e % TK : e / TM][AKF ? e / TK : e % TM] = ra[s];
     }
 #pragma unroll
-    for (int r = 0; r < (TN * TK) / THREADS; r++) {
-      const int e = tid + r * THREADS;
-      const int n = BKF ? e / TK : e % TN;
-      const int k = BKF ? e % TK : e / TN;
-      Bs[k][n] = (k0 + k < klen) ? fetch_b<T, PRIM>(p, t, k0 + k, n) : Acc(0);
+    for (int s = 0; s < LB; s++) {
+      const int e = tid + s * THREADS;
+      Bs[BKF ? e % TK : e / TN][BKF ? e / TK : e % TN] = rb[s];
     }
     __syncthreads();
+    if (k0 + TK < klen) {
+#pragma unroll
+      for (int s = 0; s < LA; s++) ra[s] = fetch_a(s, k0 + TK);
+#pragma unroll
+      for (int s = 0; s < LB; s++) rb[s] = fetch_b(s, k0 + TK);
+    }
+    const int kmax = min(TK, klen - k0);
 #pragma unroll
     for (int k = 0; k < TK; k++) {
-      Acc a[4], b[4];
+      if (k < kmax) {
+        Acc a[MR], bb[MC];
 #pragma unroll
-      for (int u = 0; u < 4; u++) a[u] = As[k][ty * 4 + u];
+        for (int u = 0; u < MR; u++) a[u] = As[k][row_of(u)];
 #pragma unroll
-      for (int v = 0; v < 4; v++) b[v] = Bs[k][tx * 4 + v];
+        for (int v = 0; v < MC; v++) bb[v] = Bs[k][col_of(v)];
 #pragma unroll
-      for (int u = 0; u < 4; u++)
+        for (int u = 0; u < MR; u++)
 #pragma unroll
-        for (int v = 0; v < 4; v++) acc[u][v] = mac<SPLIT>(a[u], b[v], acc[u][v]);
+          for (int v = 0; v < MC; v++) acc[u][v] = mac<SPLIT>(a[u], bb[v], acc[u][v]);
+      }
     }
     __syncthreads();
   }
@@ -145,28 +191,27 @@ __global__ void __launch_bounds__(THREADS) band_generic_kernel(const Problem p, 
   T *out = static_cast<T *>(p.o);
   const int W = 2 * p.w + 1;
 #pragma unroll
-  for (int u = 0; u < 4; u++) {
-    const int m = ty * 4 + u;
+  for (int u = 0; u < MR; u++) {
+    const int m = row_of(u);
 #pragma unroll
-    for (int v = 0; v < 4; v++) {
-      const int n = tx * 4 + v;
+    for (int v = 0; v < MC; v++) {
+      const int n = col_of(v);
       if (PRIM == BAND_NT) {
-        const int i = t.rt * TM + m;
-        const int j = t.ct * TN + n - m;  // = pos - off - i + w
+        const int i = rt * TM + m;
+        const int j = ct * TN + n - m;  // = pos - off - i + w
         const int pos = i + j - p.w + p.off;
         if (i < p.M && j >= 0 && j < W)
-          out[((int64_t)t.b * p.M + i) * W + j] =
-              ElemTraits<T>::store((pos >= p.lo && pos < p.hi) ? acc[u][v] : Acc(0));
+          out[((int64_t)b * p.M + i) * W + j] = ElemTraits<T>::store((pos >= p.lo && pos < p.hi) ? acc[u][v] : Acc(0));
       } else {
-        const int r = t.rt * TM + m, h = t.ct * TN + n;
+        const int r = rt * TM + m, h = ct * TN + n;
         const int rmax = (PRIM == BAND_N) ? p.M : p.Mo;
-        if (r < rmax && h < p.N) out[t.b * p.o_sb + r * p.o_sr + h * p.o_sc] = ElemTraits<T>::store(acc[u][v]);
+        if (r < rmax && h < p.N) out[b * p.o_sb + r * p.o_sr + h * p.o_sc] = ElemTraits<T>::store(acc[u][v]);
       }
     }
   }
 }
 
-template <typename T, int PRIM, bool SPLIT>
+template <typename T, int PRIM, bool SPLIT, int TM, int TN>
 cudaError_t launch_typed(const Problem &p, cudaStream_t stream) {
   int nrt, nct, klen;
   bool akf, bkf;
@@ -194,21 +239,31 @@ cudaError_t launch_typed(const Problem &p, cudaStream_t stream) {
   if (blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
   const dim3 grid((unsigned)blocks), block(THREADS);
   if (akf && bkf)
-    band_generic_kernel<T, PRIM, SPLIT, true, true><<<grid, block, 0, stream>>>(p, nrt, nct, klen);
+    band_generic_kernel<T, PRIM, SPLIT, true, true, TM, TN><<<grid, block, 0, stream>>>(p, nrt, nct, klen);
   else if (akf)
-    band_generic_kernel<T, PRIM, SPLIT, true, false><<<grid, block, 0, stream>>>(p, nrt, nct, klen);
+    band_generic_kernel<T, PRIM, SPLIT, true, false, TM, TN><<<grid, block, 0, stream>>>(p, nrt, nct, klen);
   else if (bkf)
-    band_generic_kernel<T, PRIM, SPLIT, false, true><<<grid, block, 0, stream>>>(p, nrt, nct, klen);
+    band_generic_kernel<T, PRIM, SPLIT, false, true, TM, TN><<<grid, block, 0, stream>>>(p, nrt, nct, klen);
   else
-    band_generic_kernel<T, PRIM, SPLIT, false, false><<<grid, block, 0, stream>>>(p, nrt, nct, klen);
+    band_generic_kernel<T, PRIM, SPLIT, false, false, TM, TN><<<grid, block, 0, stream>>>(p, nrt, nct, klen);
   return cudaGetLastError();
 }
 
+// Tile shapes: fp32 with enough rows gets the large tiles; everything else (fp64: registers; 16-bit inputs:
+// rarely here; short sequences: waste) the 64 x 64 ones.
 template <typename T, bool SPLIT> cudaError_t launch_prim(Primitive prim, const Problem &p, cudaStream_t s) {
+  constexpr bool F32 = sizeof(T) == 4;
+  const bool big = F32 && p.M >= 512;
   switch (prim) {
-    case BAND_NT: return launch_typed<T, BAND_NT, SPLIT>(p, s);
-    case BAND_N: return launch_typed<T, BAND_N, SPLIT>(p, s);
-    default: return launch_typed<T, BAND_T, SPLIT>(p, s);
+    case BAND_NT:
+      if (F32 && big && p.w >= 32) return launch_typed<T, BAND_NT, SPLIT, F32 ? 128 : 64, F32 ? 128 : 64>(p, s);
+      return launch_typed<T, BAND_NT, SPLIT, 64, 64>(p, s);
+    case BAND_N:
+      if (F32 && big && p.N > 32) return launch_typed<T, BAND_N, SPLIT, F32 ? 128 : 64, 64>(p, s);
+      return launch_typed<T, BAND_N, SPLIT, 64, 64>(p, s);
+    default:
+      if (F32 && big && p.N > 32) return launch_typed<T, BAND_T, SPLIT, F32 ? 128 : 64, 64>(p, s);
+      return launch_typed<T, BAND_T, SPLIT, 64, 64>(p, s);
   }
 }
 
