@@ -294,6 +294,8 @@ def run_ours(args, torch):
     q, kt, v, go = (t[b0:b1].to(dtype).contiguous() for t in (q, kt, v, go))
     host = [t.pin_memory() for t in (q, kt, v, go)]
     qd, ktd, vd, god = (t.to(dev) for t in host)
+    if args.k_layout == "bnm":  # K stored as a contiguous (B, N, M) tensor; ktd is its (B, M, N) view
+        ktd = ktd.transpose(-1, -2).contiguous().transpose(-1, -2)
     W = 2 * w + 1
     a = torch.empty(Bl, M, W, dtype=dtype, device=dev)
     ga = torch.empty_like(a)
@@ -468,7 +470,7 @@ def run_ours(args, torch):
                 "workload": workload_name(args.workload), "batch_per_gpu": per,
                 "l2": "no flush: one step touches %.0f MB per GPU, larger than the 126 MB L2" % (total_bytes / world / 1e6),
                 "launch": ("cuda graph of %d kernels, %s" % (launches_per_step, "dependency DAG" if args.branches == 2 else "one chain")) if graph is not None else "%d stream launches" % launches_per_step,
-                "k_layout": "transposed view of (B,M,N)",
+                "k_layout": "contiguous (B,N,M)" if args.k_layout == "bnm" else "transposed view of (B,M,N)",
             },
             "step_roofline": {
                 "alg_MB": round(total_bytes / 1e6, 1), "alg_GFLOP": round(total_flops / 1e9, 1),

@@ -159,6 +159,23 @@ bool make_operand_map(CUtensorMap *m, bool bf16, const void *data, int cols, int
   return r == CUDA_SUCCESS;
 }
 
+// 3-D map (positions, hidden, batch) over a 16-bit operand stored with the positions contiguous
+// (element (b, p, h) at b*stride_b + h*stride_c + p); box = (64 positions x `cols` hidden rows x 1), 128-byte swizzle.
+bool make_operand_map_mn(CUtensorMap *m, bool bf16, const void *data, int cols, int rows, int batch, int64_t stride_c,
+                         int64_t stride_b) {
+  const cuuint64_t dims[3] = {(cuuint64_t)rows, (cuuint64_t)cols, (cuuint64_t)batch};
+  const cuuint64_t strides[2] = {(cuuint64_t)stride_c * 2, (cuuint64_t)(batch > 1 ? stride_b : (int64_t)cols * stride_c) * 2};
+  const cuuint32_t box[3] = {64, (cuuint32_t)cols, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = encode_fn()(m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                                const_cast<void *>(data), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    set_launch_detail("cuTensorMapEncodeTiled(position-major operand %p, %d positions x %d, batch %d) returned %d", data, rows, cols,
+                      batch, (int)r);
+  return r == CUDA_SUCCESS;
+}
+
 // The band as a pitched matrix: x = i + j in [0, M + 2w), row i with pitch 2w elements, batch with
 // pitch M*(2w+1).  Rows overlap in memory by design (pitch < extent); an in-range (x, i, b) never
 // addresses memory outside the tensor.  Box = (64 x 128 x 1), 128-byte swizzle.
@@ -175,13 +192,25 @@ bool make_band_map(CUtensorMap *m, bool bf16, const void *band, int M, int w, in
   return r == CUDA_SUCCESS;
 }
 
+// an operand stored with the positions contiguous (stride_r == 1): hidden stride and batch stride 16-byte multiples
+bool operand_mn_tma_ok(const void *data, int64_t sb, int64_t sr, int64_t sc, int batch) {
+  return aligned16(data) && sr == 1 && sc > 0 && (sc % 8) == 0 && (batch <= 1 || (sb > 0 && (sb % 8) == 0));
+}
+
 bool operand_tma_ok(const void *data, int64_t sb, int64_t sr, int64_t sc, int batch) {
   return aligned16(data) && sc == 1 && sr > 0 && (sr % 8) == 0 && (batch <= 1 || (sb > 0 && (sb % 8) == 0));
 }
 
+// Y stored with the positions contiguous and usable through a (position, hidden, batch) map: chunk origins
+// r0 - w + off + 64k must then be multiples of 8 elements.
+bool y_position_major(const Problem &p) {
+  return !operand_tma_ok(p.b, p.b_sb, p.b_sr, p.b_sc, p.B) && operand_mn_tma_ok(p.b, p.b_sb, p.b_sr, p.b_sc, p.B) &&
+         ((p.w - p.off) % 8) == 0;
+}
+
 bool band_tma_ok(const void *band, int M, int w) { return aligned16(band) && (w % 4) == 0 && w >= 4 && (M % 8) == 0; }
 
-template <bool BF16, int NH> cudaError_t launch_nt(const Problem &p, cudaStream_t stream) {
+template <bool BF16, int NH, bool YMN> cudaError_t launch_nt(const Problem &p, cudaStream_t stream) {
   using S = NtSmem<NH>;
   using OT = KMajorTile<NH>;
   NtParams k;
@@ -191,7 +220,7 @@ template <bool BF16, int NH> cudaError_t launch_nt(const Problem &p, cudaStream_
   k.nchunks = (TILE + 2 * p.w + CHUNK - 1) / CHUNK;
   k.paired = (p.w % 64 == 0) ? 1 : 0;
   k.band = p.o;
-  auto kern = band_nt_tc_kernel<BF16, NH>;
+  auto kern = band_nt_tc_kernel<BF16, NH, YMN>;
   // the attribute is per device; setting it on every call is cheap and needs no per-device cache
   cudaError_t attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::ALLOC);
   if (attr_err != cudaSuccess) {
@@ -202,7 +231,9 @@ template <bool BF16, int NH> cudaError_t launch_nt(const Problem &p, cudaStream_
   // used for the tensor maps needs a current context (a fresh thread, e.g. an autograd worker, has none).
   CUtensorMap mx, my, mb;
   if (!make_operand_map(&mx, BF16, p.a, NH, p.M, p.B, p.a_sr, p.a_sb, OT::BOXK) ||
-      !make_operand_map(&my, BF16, p.b, NH, p.Mo, p.B, p.b_sr, p.b_sb, OT::BOXK) || !make_band_map(&mb, BF16, p.o, p.M, p.w, p.B))
+      !(YMN ? make_operand_map_mn(&my, BF16, p.b, NH, p.Mo, p.B, p.b_sc, p.b_sb)
+            : make_operand_map(&my, BF16, p.b, NH, p.Mo, p.B, p.b_sr, p.b_sb, OT::BOXK)) ||
+      !make_band_map(&mb, BF16, p.o, p.M, p.w, p.B))
     return cudaErrorInvalidValue;
   const int grid = persistent_grid(k.total_tiles);
   set_launch_detail("band_nt launch, grid %d", grid);
@@ -210,9 +241,15 @@ template <bool BF16, int NH> cudaError_t launch_nt(const Problem &p, cudaStream_
   return cudaGetLastError();
 }
 
+template <int NH> cudaError_t launch_nt_any(const Problem &p, cudaStream_t stream) {
+  const bool bf16 = p.dtype == WMM_BF16;
+  if (y_position_major(p)) return bf16 ? launch_nt<true, NH, true>(p, stream) : launch_nt<false, NH, true>(p, stream);
+  return bf16 ? launch_nt<true, NH, false>(p, stream) : launch_nt<false, NH, false>(p, stream);
+}
+
 // MODE 0 / 1: one problem (band_n / band_t).  MODE 2: `p` is the band_n problem and `pt` the band_t
 // problem over the same band (same geometry, plain: other_rows = rows, other_off = 0).
-template <bool BF16, int NH, int MODE> cudaError_t launch_mm(const Problem &p, const Problem *pt, cudaStream_t stream) {
+template <bool BF16, int NH, int MODE, bool YMN> cudaError_t launch_mm(const Problem &p, const Problem *pt, cudaStream_t stream) {
   using S = MmSmem<NH>;
   using OT = KMajorTile<NH>;
   const bool tr = MODE == 1;
@@ -223,7 +260,7 @@ template <bool BF16, int NH, int MODE> cudaError_t launch_mm(const Problem &p, c
   k.tiles_per_batch = (out_rows + TILE - 1) / TILE;
   k.total_tiles = k.tiles_per_batch * p.B;
   k.nchunks = (TILE + 2 * p.w + 127) / 128;
-  auto kern = band_mm_tc_kernel<BF16, NH, MODE>;
+  auto kern = band_mm_tc_kernel<BF16, NH, MODE, YMN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::ALLOC);
   if (e != cudaSuccess) {
     set_launch_detail("cudaFuncSetAttribute(band_mm mode %d, %d bytes of shared memory)", MODE, S::ALLOC);
@@ -232,7 +269,8 @@ template <bool BF16, int NH, int MODE> cudaError_t launch_mm(const Problem &p, c
   // (the tensor maps need the current context the runtime call above has bound to this thread)
   CUtensorMap mband, mother0, mout0, mother1, mout1;
   if (!make_band_map(&mband, BF16, p.a, p.M, p.w, p.B) ||
-      !make_operand_map(&mother0, BF16, p.b, NH, other_rows, p.B, p.b_sr, p.b_sb, OT::BOXK) ||
+      !(YMN ? make_operand_map_mn(&mother0, BF16, p.b, NH, other_rows, p.B, p.b_sc, p.b_sb)
+            : make_operand_map(&mother0, BF16, p.b, NH, other_rows, p.B, p.b_sr, p.b_sb, OT::BOXK)) ||
       !make_operand_map(&mout0, BF16, p.o, NH, out_rows, p.B, p.o_sr, p.o_sb, OT::BOXK))
     return cudaErrorInvalidValue;
   if (MODE == 2) {
@@ -251,14 +289,20 @@ template <bool BF16, int NH, int MODE> cudaError_t launch_mm(const Problem &p, c
   return cudaGetLastError();
 }
 
-template <int MODE> cudaError_t launch_mm_any(const Problem &p, const Problem *pt, cudaStream_t stream) {
+template <int MODE, bool YMN> cudaError_t launch_mm_n(const Problem &p, const Problem *pt, cudaStream_t stream) {
   const bool bf16 = p.dtype == WMM_BF16;
   switch (p.N) {
-    case 32: return bf16 ? launch_mm<true, 32, MODE>(p, pt, stream) : launch_mm<false, 32, MODE>(p, pt, stream);
-    case 64: return bf16 ? launch_mm<true, 64, MODE>(p, pt, stream) : launch_mm<false, 64, MODE>(p, pt, stream);
-    case 128: return bf16 ? launch_mm<true, 128, MODE>(p, pt, stream) : launch_mm<false, 128, MODE>(p, pt, stream);
+    case 32: return bf16 ? launch_mm<true, 32, MODE, YMN>(p, pt, stream) : launch_mm<false, 32, MODE, YMN>(p, pt, stream);
+    case 64: return bf16 ? launch_mm<true, 64, MODE, YMN>(p, pt, stream) : launch_mm<false, 64, MODE, YMN>(p, pt, stream);
+    case 128: return bf16 ? launch_mm<true, 128, MODE, YMN>(p, pt, stream) : launch_mm<false, 128, MODE, YMN>(p, pt, stream);
     default: return cudaErrorNotSupported;
   }
+}
+
+// band_n's other operand may be position-major (MODE 0 and the band_n half of MODE 2); band_t's never is here
+template <int MODE> cudaError_t launch_mm_any(const Problem &p, const Problem *pt, cudaStream_t stream) {
+  if (MODE != 1 && y_position_major(p)) return launch_mm_n<MODE, true>(p, pt, stream);
+  return launch_mm_n<MODE, false>(p, pt, stream);
 }
 
 }  // namespace
@@ -271,9 +315,10 @@ bool tensor_eligible(Primitive prim, const Problem &p) {
   switch (prim) {
     case BAND_NT:
       return band_tma_ok(p.o, p.M, p.w) && operand_tma_ok(p.a, p.a_sb, p.a_sr, p.a_sc, p.B) &&
-             operand_tma_ok(p.b, p.b_sb, p.b_sr, p.b_sc, p.B) && p.Mo > 0;
+             (operand_tma_ok(p.b, p.b_sb, p.b_sr, p.b_sc, p.B) || y_position_major(p)) && p.Mo > 0;
     case BAND_N:
-      return band_tma_ok(p.a, p.M, p.w) && operand_tma_ok(p.b, p.b_sb, p.b_sr, p.b_sc, p.B) &&
+      return band_tma_ok(p.a, p.M, p.w) &&
+             (operand_tma_ok(p.b, p.b_sb, p.b_sr, p.b_sc, p.B) || (y_position_major(p) && p.lo == 0 && p.hi == p.Mo)) &&
              operand_tma_ok(p.o, p.o_sb, p.o_sr, p.o_sc, p.B) && p.Mo > 0;
     case BAND_T:
       // the box of a tile starts at x = t0 - off + w, which must be a multiple of 8 elements (16 bytes)
@@ -285,12 +330,11 @@ bool tensor_eligible(Primitive prim, const Problem &p) {
 
 cudaError_t launch_tensor(Primitive prim, const Problem &p, cudaStream_t stream, int *launches) {
   cudaError_t e = cudaErrorNotSupported;
-  const bool bf16 = p.dtype == WMM_BF16;
   if (prim == BAND_NT) {
     switch (p.N) {
-      case 32: e = bf16 ? launch_nt<true, 32>(p, stream) : launch_nt<false, 32>(p, stream); break;
-      case 64: e = bf16 ? launch_nt<true, 64>(p, stream) : launch_nt<false, 64>(p, stream); break;
-      case 128: e = bf16 ? launch_nt<true, 128>(p, stream) : launch_nt<false, 128>(p, stream); break;
+      case 32: e = launch_nt_any<32>(p, stream); break;
+      case 64: e = launch_nt_any<64>(p, stream); break;
+      case 128: e = launch_nt_any<128>(p, stream); break;
     }
   }
   else if (prim == BAND_N)

@@ -42,7 +42,9 @@ template <int NH> struct MmSmem {
   static constexpr uint32_t TMEM_COLS = 2 * NH < 32 ? 32 : 2 * NH;  // two accumulator stages
 };
 
-template <bool BF16, int NH, int MODE>
+// YMN: the other operand of the band_n pass is stored with the POSITIONS contiguous (K given as a contiguous
+// (B, N, M) tensor): its 128-position slice is then two TMA boxes of (64 positions x NH rows), a K-major B operand.
+template <bool BF16, int NH, int MODE, bool YMN>
 __global__ void __launch_bounds__(MM_THREADS, 1)
 band_mm_tc_kernel(const __grid_constant__ CUtensorMap map_band, const __grid_constant__ CUtensorMap map_other0,
                   const __grid_constant__ CUtensorMap map_out0, const __grid_constant__ CUtensorMap map_other1,
@@ -144,9 +146,15 @@ band_mm_tc_kernel(const __grid_constant__ CUtensorMap map_band, const __grid_con
           const int orow0 = tr ? row0 : t0 - p.w + p.off + c * 128;
           tma_load_3d(band_dst, &map_band, bar_full(s), x0, row0, b);
           tma_load_3d(band_dst + BT::BOX_BYTES, &map_band, bar_full(s), x0 + 64, row0, b);
+          if (YMN && !tr) {
 #pragma unroll
-          for (int bx = 0; bx < OT::NBOX; bx++)
-            tma_load_3d(other_dst + bx * OT::BOX_BYTES, map_other, bar_full(s), bx * OT::BOXK, orow0, b);
+            for (int hf = 0; hf < 2; hf++)  // map dims: (position, hidden, batch)
+              tma_load_3d(other_dst + hf * (OT::BYTES / 2), map_other, bar_full(s), orow0 + hf * 64, 0, b);
+          } else {
+#pragma unroll
+            for (int bx = 0; bx < OT::NBOX; bx++)
+              tma_load_3d(other_dst + bx * OT::BOX_BYTES, map_other, bar_full(s), bx * OT::BOXK, orow0, b);
+          }
         }
       }
     }
@@ -163,13 +171,19 @@ band_mm_tc_kernel(const __grid_constant__ CUtensorMap map_band, const __grid_con
       constexpr uint64_t ADESC_T = smem_desc_base(BT::BOX_BYTES, 1024, 2u);
       // B operand, MN-major: OT::BOXK contiguous hidden columns per row, next box one leading offset away.
       constexpr uint64_t BDESC = smem_desc_base(OT::BOX_BYTES, 8 * OT::SW_BYTES, OT::SWZ_CODE);
+      // position-major Y (band_n pass only): K-major B, NH rows of 64 positions (128 B) per box, 8-row groups
+      // 1024 B apart, a k-step of 16 positions is 32 B further along the row, second 64 positions = second box
+      constexpr uint32_t IDESC_N_K = instr_desc_f16(BF16, false, false, TILE, NH);
+      constexpr uint64_t BDESC_K = smem_desc_base(16, 1024, 2u);
       int it = 0, tit = 0, since = 0, mk[S::STAGES];
       for (int s = 0; s < S::STAGES; s++) mk[s] = 0;
       bool ok = true;
       for (int wi = blockIdx.x; ok && wi < total_items; wi += gridDim.x, ++tit) {
         const bool tr = item_tr(wi);
         const int t0 = (item_tile(wi) % p.tiles_per_batch) * TILE;
-        const uint32_t idesc = tr ? IDESC_T : IDESC_N;
+        const bool ymn = YMN && !tr;
+        const uint32_t idesc = tr ? IDESC_T : (ymn ? IDESC_N_K : IDESC_N);
+        const uint64_t bdesc = ymn ? BDESC_K : BDESC;
         const uint64_t adesc = tr ? ADESC_T : ADESC_N;
         const int as = tit & 1;
         if (!(ok = mbar_wait(bar_acc_empty(as), ((tit >> 1) & 1) ^ 1, abort_flag))) break;
@@ -187,8 +201,8 @@ band_mm_tc_kernel(const __grid_constant__ CUtensorMap map_band, const __grid_con
 #pragma unroll
           for (int k = 0; k < 8; k++) {
             const uint32_t a_off = tr ? (uint32_t)k * 2048u : BT::kstep_offset(k);
-            const uint32_t b_off = (uint32_t)k * 16u * OT::SW_BYTES;
-            umma_f16(tmem_base + as * NH, smem_desc(adesc, a_addr + a_off), smem_desc(BDESC, b_addr + b_off), idesc,
+            const uint32_t b_off = ymn ? (uint32_t)(k >> 2) * (OT::BYTES / 2) + (uint32_t)(k & 3) * 32u : (uint32_t)k * 16u * OT::SW_BYTES;
+            umma_f16(tmem_base + as * NH, smem_desc(adesc, a_addr + a_off), smem_desc(bdesc, b_addr + b_off), idesc,
                      (c > 0 || k > 0) ? 1u : 0u);
           }
           umma_commit(bar_empty(s));
@@ -257,7 +271,7 @@ band_mm_tc_kernel(const __grid_constant__ CUtensorMap map_band, const __grid_con
           if ((lo & 7) != 0 || (g_lo == g_hi && (hi & 7) != 7)) trim_piece(g_lo);
           if (g_hi != g_lo && (hi & 7) != 7) trim_piece(g_hi);
         }
-        if (!tr) {
+        if (!tr && !YMN) {  // (a position-major operand is only taken when the whole row range is in sequence)
           // rows of the other operand whose position is outside the sequence: zero them too, so that
           // whatever sits there (an unfilled halo, Inf, NaN) cannot reach the product as 0 * x
           const int pos = t0 - p.w + p.off + c * 128 + row;

@@ -71,7 +71,10 @@ __device__ __forceinline__ void mask_columns(uint32_t (&v)[32], int kbase, int k
     if (kbase + e < kk_lo || kbase + e >= kk_hi) v[e] = 0u;
 }
 
-template <bool BF16, int NH>
+// YMN: Y is stored with the POSITIONS contiguous (K of window_matmul given as a contiguous (B, N, M) tensor, as
+// in the reference's README).  A chunk is then two TMA boxes of (64 positions x NH rows), used as an
+// MN-major B operand; otherwise Y rows are contiguous in the hidden index and the operand is K-major.
+template <bool BF16, int NH, bool YMN>
 __global__ void __launch_bounds__(NT_THREADS, 1)
 band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
                   const __grid_constant__ CUtensorMap map_band, const NtParams p) {
@@ -135,9 +138,15 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           if (!(ok = mbar_wait(bar_k_empty(ks), ((kit / S::KS) & 1) ^ 1, abort_flag))) break;
           mbar_expect_tx(bar_k_full(ks), OT::BYTES);
           const int p0 = r0 - p.w + p.off + chunk_at(k) * CHUNK;
+          if (YMN) {
 #pragma unroll
-          for (int bx = 0; bx < OT::NBOX; bx++)
-            tma_load_3d(base + S::OFF_K + ks * OT::BYTES + bx * OT::BOX_BYTES, &map_y, bar_k_full(ks), bx * OT::BOXK, p0, b);
+            for (int hf = 0; hf < 2; hf++)  // map dims: (position, hidden, batch)
+              tma_load_3d(base + S::OFF_K + ks * OT::BYTES + hf * (OT::BYTES / 2), &map_y, bar_k_full(ks), p0 + hf * HALF, 0, b);
+          } else {
+#pragma unroll
+            for (int bx = 0; bx < OT::NBOX; bx++)
+              tma_load_3d(base + S::OFF_K + ks * OT::BYTES + bx * OT::BOX_BYTES, &map_y, bar_k_full(ks), bx * OT::BOXK, p0, b);
+          }
         }
       }
     }
@@ -147,18 +156,22 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     // epilogue groups consume; 8 stages.  With pairing the first and last chunk are interleaved half by
     // half, so that each merged half-box finds both its triangles in TMEM.
     if (lane == 0) {
-      constexpr uint32_t IDESC = instr_desc_f16(BF16, false, false, TILE, HALF);
+      constexpr uint32_t IDESC = instr_desc_f16(BF16, false, YMN, TILE, HALF);
+      // MN-major Y: one box = NH rows (hidden) of 64 positions (128 B); 8-row groups 1024 B apart, a k-step of
+      // 16 hidden rows is 2048 B further; the second 64 positions of the chunk are the second box.
+      constexpr uint64_t YDESC = YMN ? smem_desc_base(OT::BYTES / 2, 1024, 2u) : OT::DESC;
       int qit = 0, kit = 0, ait = 0;
       bool ok = true;
       auto half_mma = [&](uint32_t q_addr, uint32_t k_addr, int half) -> bool {
         const int as = ait % ACC_STAGES;
         if (!mbar_wait(bar_acc_empty(as), ((ait / ACC_STAGES) & 1) ^ 1, abort_flag)) return false;
         tc_fence_after_sync();
-        const uint32_t b_addr = k_addr + half * HALF * OT::SW_BYTES;  // rows 64*half .. of every box
+        // K-major: rows 64*half .. of every box; MN-major: box `half`
+        const uint32_t b_addr = k_addr + (YMN ? half * (OT::BYTES / 2) : half * HALF * OT::SW_BYTES);
 #pragma unroll
         for (int s = 0; s < OT::KSTEPS; s++)
           umma_f16(tmem_base + as * HALF, smem_desc(OT::DESC, q_addr + OT::kstep_offset(s)),
-                   smem_desc(OT::DESC, b_addr + OT::kstep_offset(s)), IDESC, s > 0 ? 1u : 0u);
+                   smem_desc(YDESC, b_addr + (YMN ? (uint32_t)s * 2048u : OT::kstep_offset(s))), IDESC, s > 0 ? 1u : 0u);
         umma_commit(bar_acc_full(as));
         ++ait;
         return true;

@@ -230,6 +230,38 @@ def test_small_window_family_on_a_sequence_shard(wm):
     H.assert_lowp_close(torch.from_numpy(gv[:, w:w + M]), want["gv"], "gv summed over shards")
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [s for s in SHAPES if s[3] % 8 == 0 and s[3] > 32])
+def test_k_as_contiguous_bnm_tensor_takes_the_tensor_path(wm, shape, dtype):
+    """K given as a contiguous (B, N, M) tensor (as in the reference's README example): consumed in place by the
+    tcgen05 kernels (position-major operand), forward and both gradients, no transposing copy."""
+    from window_matmul import _native as N
+
+    B, M, Nn, w = shape
+    d = _inputs(shape, dtype)
+    k_np = np.ascontiguousarray(d["kt"].transpose(0, 2, 1))
+    want_a = H.oracle.window_matmul_forward(d["q"], k_np, w)
+    want_gq, want_gk = H.oracle.window_matmul_backward(d["q"], k_np, w, d["g_band"])
+    q, g_band = H.to_dev(d["q"], dtype), H.to_dev(d["g_band"], dtype)
+    k = H.to_dev(k_np, dtype)
+    assert k.is_contiguous() and k.shape == (B, Nn, M)
+    old = wm.set_flags(N.FLAG_REQUIRE_TENSOR)
+    try:
+        a = wm.window_matmul_forward(q, k, w)
+        before = N.launch_count()
+        gq, gk = wm.window_matmul_backward(q, k, w, g_band)
+        assert N.launch_count() - before == 1
+        gq_only, _ = wm.window_matmul_backward(q, k, w, g_band, need=(True, False))
+    finally:
+        wm.set_flags(old)
+    torch.cuda.synchronize()
+    assert N.device_status() == 0 and gk.shape == (B, Nn, M)
+    H.assert_lowp_close(a, want_a, "a")
+    H.assert_lowp_close(gq, want_gq, "grad_q")
+    H.assert_lowp_close(gq_only, want_gq, "grad_q (band_n alone)")
+    H.assert_lowp_close(gk, want_gk, "grad_k")
+
+
 def test_ineligible_problems_are_reported_not_faked(wm):
     from window_matmul import _native as N
 
