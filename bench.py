@@ -286,6 +286,8 @@ def run_ours(args, torch):
     B, M, N, w, dt, distn = WORKLOADS[args.workload]
     dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[dt]
     e = 2 if dt != "fp32" else 4
+    if args.shard == "seq" or (args.shard == "auto" and args.workload == "c4" and world > 1):
+        return run_seq_sharded(args, torch, impl, N_, rank, world, dev)
     # strong scaling: the same B sequences, split evenly over the ranks (the last rank may get fewer)
     per = (B + world - 1) // world
     b0, b1 = min(B, rank * per), min(B, (rank + 1) * per)
@@ -511,6 +513,98 @@ def run_ours(args, torch):
         dist.destroy_process_group()
 
 
+def run_seq_sharded(args, torch, impl, N_, rank, world, dev):
+    """Sequence-sharded step (config 4): rank r owns rows [r*M/P, (r+1)*M/P) of every tensor; K^T and V rows
+    within w of a shard edge are exchanged with the neighbours before the forward contractions, partial
+    grad_K / grad_V rows after the backward ones (window_matmul/sharded.py).  Same six contractions, same
+    job at every P (strong scaling); time = max over ranks on device clocks."""
+    import torch.distributed as dist
+
+    from window_matmul import sharded
+
+    B, M, N, w, dt, distn = WORKLOADS[args.workload]
+    dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[dt]
+    e = 2 if dt != "fp32" else 4
+    Ml = M // world
+    g = torch.Generator(device="cpu").manual_seed(rank)
+    s = 1.0 / N ** 0.5 if distn == "normal_scaled" else 1.0
+    q = (torch.randn(B, Ml, N, generator=g) * s).to(dtype).to(dev)
+    # K^T and V live in storage with halo margins, so the exchange writes only the margins
+    kt, _ = sharded.alloc_with_halo(B, Ml, N, w, dtype, dev)
+    v, _ = sharded.alloc_with_halo(B, Ml, N, w, dtype, dev)
+    kt.copy_((torch.randn(B, Ml, N, generator=g) * s).to(dtype))
+    v.copy_((torch.randn(B, Ml, N, generator=g) * s).to(dtype))
+    go = torch.randn(B, Ml, N, generator=g).to(dtype).to(dev)
+    W = 2 * w + 1
+    a = torch.empty(B, Ml, W, dtype=dtype, device=dev)
+    ga = torch.empty_like(a)
+    o, gq = torch.empty_like(q), torch.empty_like(q)
+    seq = sharded._local_seq(Ml, w, None) if world > 1 else (0, Ml)
+    ext = Ml + 2 * w if world > 1 else Ml
+    off = w if world > 1 else 0
+    halo = (lambda x: sharded.exchange_halo(x, w)) if world > 1 else (lambda x: x)
+    unhalo = (lambda x: sharded.reduce_halo(x, w)) if world > 1 else (lambda x: x)
+
+    # The exchanges run in stream order between the kernels.  Overlapping them on a second stream measured
+    # slower: the contraction kernels are persistent (one CTA per SM for the whole launch), so a concurrent
+    # NCCL kernel waits for an SM until they finish.
+    def step():
+        kt_ext = halo(kt)
+        impl.band_nt(q, kt_ext, w, other_off=off, seq=seq, out=a)
+        v_ext = halo(v)
+        impl.band_n(a, v_ext, w, other_off=off, seq=seq, out=o)
+        impl.band_nt(go, v_ext, w, other_off=off, seq=seq, out=ga)
+        gv = unhalo(impl.band_t(a, go, w, other_rows=ext, other_off=off, seq=seq))
+        impl.band_n(ga, kt_ext, w, other_off=off, seq=seq, out=gq)
+        gk = unhalo(impl.band_t(ga, q, w, other_rows=ext, other_off=off, seq=seq))
+        return gv, gk
+
+    def barrier():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    barrier()
+    launches0 = N_.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(dev.index) as clocks:
+        ev0.record()
+        for _ in range(args.steps):
+            step()
+        ev1.record()
+        torch.cuda.synchronize(dev)
+    barrier()
+    launches = N_.launch_count() - launches0
+    if N_.device_status() != 0:
+        raise SystemExit("bench.py: a kernel abandoned a bounded wait; numbers are void")
+    t = torch.tensor([ev0.elapsed_time(ev1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    us = float(t[0]) * 1e3 / args.steps
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        total_bytes, total_flops = algorithmic(B, M, N, w, e)
+        halo_bytes = 0 if world == 1 else 4 * 2 * B * w * N * e  # per interior rank and step: K^T, V out and grad halos back
+        line = {
+            "metric": "fwd+bwd window+unwindow us (%s, sequence-sharded)" % args.workload, "value": us, "unit": "us", "n_gpus": world,
+            "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": us / 1e3, "higher_is_better": False,
+            "scaling": "strong", "vs_baseline": None, "dtype": dt.replace("fp", "f"), "data": "synthetic",
+            "config": {"workload": workload_name(args.workload), "parallelism": "sequence-sharded x%d, w-row halo exchange (NCCL send/recv)" % world,
+                       "rows_per_gpu": Ml, "halo_bytes_per_rank_step": halo_bytes, "launch": "stream launches",
+                       "l2": "no flush: one step touches %.0f MB per GPU" % (total_bytes / world / 1e6)},
+            "step_roofline": {"alg_MB": round(total_bytes / 1e6, 1), "alg_GFLOP": round(total_flops / 1e9, 1),
+                              "achieved_GBps": round(total_bytes / (us * 1e-6) / 1e9, 1),
+                              "frac_of_%s_hbm" % peak_kind: round(total_bytes / world / (us * 1e-6) / 1e9 / peak, 4)},
+            "gpu_launches": int(launches), "clocks": clocks.summary(),
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -522,6 +616,10 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch the six kernels on the stream instead of a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=0, help="override B of the workload (small cases for profiling)")
+    ap.add_argument("--k-layout", default="view", choices=["view", "bnm"],
+                    help="K as a transposed view of a (B,M,N) tensor (default) or as a contiguous (B,N,M) tensor")
+    ap.add_argument("--shard", default="auto", choices=["auto", "batch", "seq"],
+                    help="multi-GPU partitioning: batch entries (default) or sequence rows with halo exchange (default for c4)")
     ap.add_argument("--e2e-chunks", type=int, default=8, help="batch chunks of the host-buffer leg")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     args = ap.parse_args()
