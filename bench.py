@@ -542,22 +542,22 @@ def run_seq_sharded(args, torch, impl, N_, rank, world, dev):
     seq = sharded._local_seq(Ml, w, None) if world > 1 else (0, Ml)
     ext = Ml + 2 * w if world > 1 else Ml
     off = w if world > 1 else 0
-    halo = (lambda x: sharded.exchange_halo(x, w)) if world > 1 else (lambda x: x)
-    unhalo = (lambda x: sharded.reduce_halo(x, w)) if world > 1 else (lambda x: x)
+    halo = (lambda xs: sharded.exchange_halo_many(xs, w)) if world > 1 else (lambda xs: xs)
+    unhalo = (lambda xs: sharded.reduce_halo_many(xs, w)) if world > 1 else (lambda xs: xs)
 
-    # The exchanges run in stream order between the kernels.  Overlapping them on a second stream measured
-    # slower: the contraction kernels are persistent (one CTA per SM for the whole launch), so a concurrent
-    # NCCL kernel waits for an SM until they finish.
+    # Two neighbour exchanges per step: the K^T and V halos together before the forward contractions, the
+    # partial grad_V and grad_K rows together after the backward ones.  They run in stream order: overlapping
+    # them on a second stream measured slower, because the contraction kernels are persistent (one CTA per
+    # SM for the whole launch) and a concurrent NCCL kernel waits for an SM until they finish.
     def step():
-        kt_ext = halo(kt)
+        kt_ext, v_ext = halo([kt, v])
         impl.band_nt(q, kt_ext, w, other_off=off, seq=seq, out=a)
-        v_ext = halo(v)
         impl.band_n(a, v_ext, w, other_off=off, seq=seq, out=o)
         impl.band_nt(go, v_ext, w, other_off=off, seq=seq, out=ga)
-        gv = unhalo(impl.band_t(a, go, w, other_rows=ext, other_off=off, seq=seq))
+        gv_part = impl.band_t(a, go, w, other_rows=ext, other_off=off, seq=seq)
         impl.band_n(ga, kt_ext, w, other_off=off, seq=seq, out=gq)
-        gk = unhalo(impl.band_t(ga, q, w, other_rows=ext, other_off=off, seq=seq))
-        return gv, gk
+        gk_part = impl.band_t(ga, q, w, other_rows=ext, other_off=off, seq=seq)
+        return unhalo([gv_part, gk_part])
 
     def barrier():
         torch.cuda.synchronize(dev)

@@ -61,69 +61,86 @@ def alloc_with_halo(batch: int, rows: int, cols: int, window: int, dtype, device
     return local, ext
 
 
+def _extended(x: torch.Tensor, window: int) -> torch.Tensor:
+    """The (B, Ml + 2w, N) buffer whose middle rows are x: x's own storage if it came from alloc_with_halo(),
+    else a new zeroed buffer with x copied in."""
+    B, Ml, N = x.shape
+    held = _HALO_STORAGE.get(x.data_ptr())
+    if held is not None and held[1] == window and held[0].shape == (B, Ml + 2 * window, N) and held[0].dtype == x.dtype \
+            and x.stride() == held[0][:, window:window + Ml].stride():
+        return held[0]
+    ext = x.new_zeros((B, Ml + 2 * window, N))
+    ext[:, window:window + Ml] = x
+    return ext
+
+
+def _swap_strips(to_lo, to_hi, group):
+    """One neighbour exchange: sends `to_lo` to the lower and `to_hi` to the upper neighbour (contiguous
+    tensors, or None at a sequence end) and returns what they sent (same shapes), or None."""
+    _, _, lo, hi = _neighbours(group)
+    ops, from_lo, from_hi = [], None, None
+    if lo is not None:
+        from_lo = torch.empty_like(to_lo)
+        ops += [dist.P2POp(dist.isend, to_lo, lo, group), dist.P2POp(dist.irecv, from_lo, lo, group)]
+    if hi is not None:
+        from_hi = torch.empty_like(to_hi)
+        ops += [dist.P2POp(dist.isend, to_hi, hi, group), dist.P2POp(dist.irecv, from_hi, hi, group)]
+    if ops:
+        for req in dist.batch_isend_irecv(ops):
+            req.wait()
+    return from_lo, from_hi
+
+
+def exchange_halo_many(xs, window: int, group=None):
+    """exchange_halo() for several tensors of the same shape and dtype in ONE neighbour exchange (their
+    boundary rows travel in one message per direction).  Returns the extended tensors."""
+    B, Ml, N = xs[0].shape
+    if Ml < window:
+        raise RuntimeError("sequence shard of %d rows is shorter than the window %d" % (Ml, window))
+    _, _, lo, hi = _neighbours(group)
+    exts = [_extended(x, window) for x in xs]
+    to_lo = torch.stack([x[:, :window] for x in xs]) if lo is not None else None
+    to_hi = torch.stack([x[:, Ml - window:] for x in xs]) if hi is not None else None
+    from_lo, from_hi = _swap_strips(to_lo, to_hi, group)
+    for i, ext in enumerate(exts):
+        if from_lo is not None:
+            ext[:, :window] = from_lo[i]
+        if from_hi is not None:
+            ext[:, window + Ml:] = from_hi[i]
+    return exts
+
+
 def exchange_halo(x: torch.Tensor, window: int, group=None) -> torch.Tensor:
     """x (B, Ml, N) local rows -> (B, Ml + 2w, N): [w rows of the lower neighbour | x | w rows of the upper
     neighbour]; zeros where the global sequence ends.  If x lives in storage from alloc_with_halo() only the
     margins are written; otherwise x is copied into a new extended buffer."""
-    B, Ml, N = x.shape
-    if Ml < window:
-        raise RuntimeError("sequence shard of %d rows is shorter than the window %d" % (Ml, window))
+    return exchange_halo_many([x], window, group)[0]
+
+
+def reduce_halo_many(parts, window: int, group=None):
+    """reduce_halo() for several tensors of the same shape and dtype in ONE neighbour exchange."""
+    B, Mext, N = parts[0].shape
+    Ml = Mext - 2 * window
     _, _, lo, hi = _neighbours(group)
-    held = _HALO_STORAGE.get(x.data_ptr())
-    if held is not None and held[1] == window and held[0].shape == (B, Ml + 2 * window, N) and held[0].dtype == x.dtype \
-            and x.stride() == held[0][:, window:window + Ml].stride():
-        ext = held[0]
-    else:
-        ext = x.new_zeros((B, Ml + 2 * window, N))
-        ext[:, window:window + Ml] = x
-    ops, keep = [], []
-    if lo is not None:
-        head = x[:, :window].contiguous()
-        recv_lo = x.new_empty((B, window, N))
-        keep += [head, recv_lo]
-        ops += [dist.P2POp(dist.isend, head, lo, group), dist.P2POp(dist.irecv, recv_lo, lo, group)]
-    if hi is not None:
-        tail = x[:, Ml - window:].contiguous()
-        recv_hi = x.new_empty((B, window, N))
-        keep += [tail, recv_hi]
-        ops += [dist.P2POp(dist.isend, tail, hi, group), dist.P2POp(dist.irecv, recv_hi, hi, group)]
-    if ops:
-        for req in dist.batch_isend_irecv(ops):
-            req.wait()
-    if lo is not None:
-        ext[:, :window] = recv_lo
-    if hi is not None:
-        ext[:, window + Ml:] = recv_hi
-    return ext
+    to_lo = torch.stack([p_[:, :window] for p_ in parts]) if lo is not None else None
+    to_hi = torch.stack([p_[:, window + Ml:] for p_ in parts]) if hi is not None else None
+    from_lo, from_hi = _swap_strips(to_lo, to_hi, group)
+    owns = []
+    for i, p_ in enumerate(parts):
+        own = p_[:, window:window + Ml]
+        if from_lo is not None:
+            own[:, :window] += from_lo[i]
+        if from_hi is not None:
+            own[:, Ml - window:] += from_hi[i]
+        owns.append(own)
+    return owns
 
 
 def reduce_halo(part: torch.Tensor, window: int, group=None) -> torch.Tensor:
     """part (B, Ml + 2w, N): this rank's contributions to positions [m0 - w, m0 + Ml + w).  Sends the two
     halo strips to the neighbours that own those positions and adds what they send, in place: returns the
     (B, Ml, N) view part[:, w:w+Ml]."""
-    B, Mext, N = part.shape
-    Ml = Mext - 2 * window
-    _, _, lo, hi = _neighbours(group)
-    own = part[:, window:window + Ml]
-    ops, bufs = [], {}
-    if lo is not None:
-        send = part[:, :window].contiguous()
-        bufs["lo"] = part.new_empty((B, window, N))
-        bufs["lo_send"] = send
-        ops += [dist.P2POp(dist.isend, send, lo, group), dist.P2POp(dist.irecv, bufs["lo"], lo, group)]
-    if hi is not None:
-        send = part[:, window + Ml:].contiguous()
-        bufs["hi"] = part.new_empty((B, window, N))
-        bufs["hi_send"] = send
-        ops += [dist.P2POp(dist.isend, send, hi, group), dist.P2POp(dist.irecv, bufs["hi"], hi, group)]
-    if ops:
-        for req in dist.batch_isend_irecv(ops):
-            req.wait()
-    if lo is not None:
-        own[:, :window] += bufs["lo"]
-    if hi is not None:
-        own[:, Ml - window:] += bufs["hi"]
-    return own
+    return reduce_halo_many([part], window, group)[0]
 
 
 def _local_seq(Ml: int, window: int, group) -> Tuple[int, int]:
