@@ -77,7 +77,11 @@ enum {
   WMM_FLAG_FORCE_GENERIC = 1u << 1,
   /* fail with WMM_ERR_UNSUPPORTED instead of taking the CUDA-core kernels (testing the fast paths:
    * families 1 and 2 of wmm_query_path). */
-  WMM_FLAG_REQUIRE_TENSOR = 1u << 2
+  WMM_FLAG_REQUIRE_TENSOR = 1u << 2,
+  /* wmm_band_softmax / wmm_band_softmax_bwd only: out-of-sequence slots take part in the softmax with the score
+   * stored there (window_matmul writes 0), which is what a plain torch softmax over the band does
+   * (tests/test_attention.py:60-61).  Without this flag those slots get probability exactly 0. */
+  WMM_FLAG_SOFTMAX_KEEP_PADDING = 1u << 3
 };
 
 /* A (batch, rows, cols) operand addressed by ELEMENT strides: either of the two inner strides may be
@@ -156,6 +160,22 @@ WMM_API int wmm_window_bwd(const wmm_operand *q, const wmm_operand *kt, const vo
 WMM_API int wmm_unwindow_bwd(const void *band, const wmm_operand *v, const wmm_operand *grad_o, void *grad_band,
                      const wmm_operand *grad_v, const wmm_geometry *g, int dtype, unsigned flags,
                      void *stream);
+
+/* ---- softmax over the band (between the two operators) ------------------------------------------ */
+
+/* probs[b,i,:] = softmax_j(scale * scores[b,i,j]) over the slots j whose position i + j - window + other_off lies in
+ * [seq_lo, seq_hi); the other slots get probability 0 (or take part, WMM_FLAG_SOFTMAX_KEEP_PADDING).  One pass over
+ * HBM; `probs` may equal `scores`.  Both are contiguous (batch, rows, 2*window+1), 16-byte aligned; g->cols is not
+ * used.  Replaces the torch ops a caller of the reference puts between the two operators
+ * (tests/test_attention.py:60-61: `att_scores / sqrt(N)`, `softmax(att_scores, dim=-1)`), plus the -inf mask for
+ * the out-of-sequence slots that the reference leaves to the caller. */
+WMM_API int wmm_band_softmax(const void *scores, void *probs, const wmm_geometry *g, int dtype, float scale,
+                             unsigned flags, void *stream);
+
+/* grad_scores = scale * probs * (grad_probs - sum_j grad_probs * probs), slot rule as in the forward.
+ * `grad_scores` may equal `grad_probs`. */
+WMM_API int wmm_band_softmax_bwd(const void *probs, const void *grad_probs, void *grad_scores,
+                                 const wmm_geometry *g, int dtype, float scale, unsigned flags, void *stream);
 
 #ifdef __cplusplus
 }

@@ -97,3 +97,26 @@ def chain_fwd_bwd(q, k, v, w, gout):
     ga, gv = unwindow_matmul_backward(a, v, w, gout)
     gq, gk = window_matmul_backward(q, k, w, ga)
     return a, o, gq, gk, ga, gv
+
+
+def band_softmax(scores, scale=1.0, mask=True):
+    """float64 softmax over the band (any leading dims folded into B): scores (B,M,2w+1) -> probabilities."""
+    x = _c(scores, np.float64)
+    B, M, W = x.shape
+    out = np.empty_like(x)
+    f = _lib().wmm_oracle_band_softmax_f64
+    f.restype = None
+    f(_p(x), _p(out), ctypes.c_long(B), ctypes.c_long(M), ctypes.c_long((W - 1) // 2), ctypes.c_double(scale),
+      ctypes.c_int(1 if mask else 0))
+    return out
+
+
+def band_softmax_backward(probs, grad_probs, scale=1.0, mask=True):
+    p, g = _c(probs, np.float64), _c(grad_probs, np.float64)
+    B, M, W = p.shape
+    out = np.empty_like(p)
+    f = _lib().wmm_oracle_band_softmax_bw_f64
+    f.restype = None
+    f(_p(p), _p(g), _p(out), ctypes.c_long(B), ctypes.c_long(M), ctypes.c_long((W - 1) // 2), ctypes.c_double(scale),
+      ctypes.c_int(1 if mask else 0))
+    return out

@@ -21,6 +21,7 @@
  * Parity pin: tests/test_oracle.py checks these functions bit for bit against golden vectors produced
  * by the compiled reference itself (tests/golden/make_golden.py).
  */
+#include <math.h>
 #include <stddef.h>
 #include <string.h>
 
@@ -107,4 +108,44 @@ WMM_DEFINE(float, f32, MUL_NATIVE, ADD_NATIVE)
 WMM_DEFINE(double, f64, MUL_NATIVE, ADD_NATIVE)
 WMM_DEFINE(_Float16, f16, MUL_HALF, ADD_HALF)
 
-int wmm_oracle_abi_version(void) { return 1; }
+/*
+ * Softmax over the band between the two operators, in double precision.  The reference ships no such
+ * function: its callers compose it from torch ops (tests/test_attention.py:60-61, scores / sqrt(N), then
+ * softmax over the last dimension); mask == 0 restates exactly that composition (every slot takes part
+ * with the score stored there), mask != 0 is the same after setting the out-of-sequence slots (position
+ * i + j - w outside [0, M)) to -inf, i.e. probability 0.  Pinned by tests/test_oracle.py against torch's
+ * CPU softmax of the same composition.
+ */
+void wmm_oracle_band_softmax_f64(const double *scores, double *probs, long B, long M, long w, double scale,
+                                 int mask) {
+  const long W = 2 * w + 1;
+  for (long r = 0; r < B * M; ++r) {
+    const long i = r % M;
+    const long jlo = mask ? WMM_MAX(0, w - i) : 0;
+    const long jhi = mask ? WMM_MIN(W, M - i + w) : W;
+    const double *x = scores + (size_t)r * W;
+    double *p = probs + (size_t)r * W;
+    double mx = -INFINITY, sum = 0.0;
+    for (long j = jlo; j < jhi; ++j) mx = WMM_MAX(mx, x[j] * scale);
+    for (long j = jlo; j < jhi; ++j) sum += exp(x[j] * scale - mx);
+    for (long j = 0; j < W; ++j) p[j] = (j >= jlo && j < jhi) ? exp(x[j] * scale - mx) / sum : 0.0;
+  }
+}
+
+/* grad_scores = scale * p * (grad_p - sum_j grad_p * p) over the slots that took part. */
+void wmm_oracle_band_softmax_bw_f64(const double *probs, const double *gprobs, double *gscores, long B, long M,
+                                    long w, double scale, int mask) {
+  const long W = 2 * w + 1;
+  for (long r = 0; r < B * M; ++r) {
+    const long i = r % M;
+    const long jlo = mask ? WMM_MAX(0, w - i) : 0;
+    const long jhi = mask ? WMM_MIN(W, M - i + w) : W;
+    const double *p = probs + (size_t)r * W, *g = gprobs + (size_t)r * W;
+    double *o = gscores + (size_t)r * W;
+    double dot = 0.0;
+    for (long j = jlo; j < jhi; ++j) dot += p[j] * g[j];
+    for (long j = 0; j < W; ++j) o[j] = (j >= jlo && j < jhi) ? scale * p[j] * (g[j] - dot) : 0.0;
+  }
+}
+
+int wmm_oracle_abi_version(void) { return 2; }

@@ -195,6 +195,34 @@ const char *wmm_status_string(int status) {
   }
 }
 
+static int band_softmax_common(bool backward, const void *in, const void *in2, void *out, const wmm_geometry *g,
+                               int dtype, float scale, unsigned flags, void *stream) {
+  if (int s = check_geometry(g, dtype, 0u)) return s;
+  if (flags & ~(unsigned)WMM_FLAG_SOFTMAX_KEEP_PADDING)
+    return fail(WMM_ERR_UNSUPPORTED, "the band softmax takes no flag but WMM_FLAG_SOFTMAX_KEEP_PADDING");
+  if ((int64_t)g->batch * g->rows == 0) return WMM_OK;
+  if (!in || !out || (backward && !in2)) return fail(WMM_ERR_NULL, "a band pointer is NULL");
+  if (((uintptr_t)in | (uintptr_t)out | (uintptr_t)in2) & 15)
+    return fail(WMM_ERR_STRIDE, "band tensors of the softmax must be 16-byte aligned");
+  if (!(scale == scale)) return fail(WMM_ERR_SHAPE, "Input mismatch: scale is NaN");
+  int launches = 0;
+  cudaError_t e = wmm::launch_band_softmax(backward, in, in2, out, *g, dtype, scale,
+                                           !(flags & WMM_FLAG_SOFTMAX_KEEP_PADDING), (cudaStream_t)stream, &launches);
+  g_launches.fetch_add((uint64_t)launches, std::memory_order_relaxed);
+  if (e != cudaSuccess) return fail(WMM_ERR_CUDA, "CUDA error launching the band softmax: %s", cudaGetErrorString(e));
+  return WMM_OK;
+}
+
+int wmm_band_softmax(const void *scores, void *probs, const wmm_geometry *g, int dtype, float scale, unsigned flags,
+                     void *stream) {
+  return band_softmax_common(false, scores, nullptr, probs, g, dtype, scale, flags, stream);
+}
+
+int wmm_band_softmax_bwd(const void *probs, const void *grad_probs, void *grad_scores, const wmm_geometry *g,
+                         int dtype, float scale, unsigned flags, void *stream) {
+  return band_softmax_common(true, probs, grad_probs, grad_scores, g, dtype, scale, flags, stream);
+}
+
 uint64_t wmm_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int64_t wmm_device_status(int clear) {

@@ -44,6 +44,10 @@ cudaError_t launch_tensor_fused_pair(const Problem &pn, const Problem &pt, cudaS
 bool small_eligible(Primitive prim, const Problem &p);
 cudaError_t launch_small(Primitive prim, const Problem &p, cudaStream_t stream, int *launches);
 
+// Masked, scaled softmax over band rows (forward: in = scores; backward: in = probabilities, in2 = their gradient).
+cudaError_t launch_band_softmax(bool backward, const void *in, const void *in2, void *out, const wmm_geometry &g,
+                                int dtype, float scale, bool mask, cudaStream_t stream, int *launches);
+
 // Launchers describe a failure (which step, which driver code) here; the API layer appends it to the
 // error string of the calling thread.
 void set_launch_detail(const char *fmt, ...);

@@ -16,6 +16,7 @@ F16, BF16, F32, F64 = 0, 1, 2, 3
 FLAG_SPLIT_ROUNDING = 1 << 0
 FLAG_FORCE_GENERIC = 1 << 1
 FLAG_REQUIRE_TENSOR = 1 << 2
+FLAG_SOFTMAX_KEEP_PADDING = 1 << 3
 BAND_NT, BAND_N, BAND_T = 1, 2, 3
 
 _DTYPES = {torch.float16: F16, torch.bfloat16: BF16, torch.float32: F32, torch.float64: F64}
@@ -74,6 +75,10 @@ def _load():
     lib.wmm_window_bwd.argtypes = [P(Operand), P(Operand), vp, P(Operand), P(Operand), P(Geometry), i32, u32, vp]
     lib.wmm_unwindow_bwd.restype = i32
     lib.wmm_unwindow_bwd.argtypes = [vp, P(Operand), P(Operand), vp, P(Operand), P(Geometry), i32, u32, vp]
+    lib.wmm_band_softmax.restype = i32
+    lib.wmm_band_softmax.argtypes = [vp, vp, P(Geometry), i32, ctypes.c_float, u32, vp]
+    lib.wmm_band_softmax_bwd.restype = i32
+    lib.wmm_band_softmax_bwd.argtypes = [vp, vp, vp, P(Geometry), i32, ctypes.c_float, u32, vp]
     if lib.wmm_version() != 1:
         raise RuntimeError("window_matmul: %s has ABI version %d, expected 1" % (LIB_PATH, lib.wmm_version()))
     return lib

@@ -67,9 +67,14 @@ def test_python_surface_matches_the_reference():
 
     import window_matmul as wm
 
-    assert wm.__all__ == ["window_matmul", "unwindow_matmul"]
+    # the reference's two names (window_matmul/__init__.py:2-4) first, unchanged; the band softmax is an addition
+    assert wm.__all__[:2] == ["window_matmul", "unwindow_matmul"]
+    assert wm.__all__[2:] == ["window_softmax"]
     for fn in (wm.window_matmul, wm.unwindow_matmul):
         assert list(inspect.signature(fn).parameters) == ["inp", "other", "window_size"]
+    assert list(inspect.signature(wm.window_softmax).parameters) == ["scores", "scale", "mask"]
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        wm.window_softmax(__import__("torch").zeros(1, 4, 9))
 
 
 def test_cpu_tensors_are_refused_loudly():

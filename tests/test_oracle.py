@@ -97,3 +97,32 @@ def test_oracle_ignores_out_of_sequence_band_input():
             if not 0 <= i + j - w < M:
                 poisoned[:, i, j] = np.nan
     assert np.array_equal(oracle.unwindow_matmul_forward(att, v, w), oracle.unwindow_matmul_forward(poisoned, v, w))
+
+
+@pytest.mark.parametrize("mask", [False, True])
+@pytest.mark.parametrize("M,w", [(7, 3), (16, 16), (33, 5), (5, 9)])
+def test_oracle_band_softmax_matches_the_torch_composition(M, w, mask):
+    """The reference composes the step between its two operators from torch ops (tests/test_attention.py:60-61:
+    scores / sqrt(N), softmax over the last dimension); the oracle's softmax is pinned to that composition on CPU,
+    forward and (through autograd) backward."""
+    import torch
+
+    g = torch.Generator().manual_seed(M * 100 + w)
+    B, W = 2, 2 * w + 1
+    scores = torch.randn(B, M, W, generator=g, dtype=torch.float64, requires_grad=True)
+    gp = torch.randn(B, M, W, generator=g, dtype=torch.float64)
+    scale = 1.0 / 8.0
+    s = scores * scale
+    if mask:
+        i = torch.arange(M)[:, None]
+        j = torch.arange(W)[None, :]
+        outside = ((i + j - w) < 0) | ((i + j - w) >= M)
+        s = s.masked_fill(outside, float("-inf"))
+    p = torch.softmax(s, dim=-1)
+    p.backward(gp)
+    po = oracle.band_softmax(scores.detach().numpy(), scale, mask)
+    np.testing.assert_allclose(po, p.detach().numpy(), rtol=1e-13, atol=1e-15)
+    go = oracle.band_softmax_backward(po, gp.numpy(), scale, mask)
+    np.testing.assert_allclose(go, scores.grad.numpy(), rtol=1e-12, atol=1e-15)
+    if mask:
+        assert (po[:, outside.numpy()] == 0).all() and (go[:, outside.numpy()] == 0).all()
