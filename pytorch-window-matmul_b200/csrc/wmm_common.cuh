@@ -56,6 +56,8 @@ const char *launch_detail();
 // Device-side status word: a kernel that abandons a bounded wait ORs a code into it.  Synchronises the
 // current device, copies the word out and optionally clears it.
 cudaError_t read_device_status(unsigned long long *word, bool clear);
+// Address of that word on the current device (for kernels of other translation units); NULL on failure.
+unsigned long long *device_status_word();
 
 template <typename T> struct ElemTraits;
 template <> struct ElemTraits<float> {

@@ -34,6 +34,11 @@ cudaError_t read_device_status(unsigned long long *word, bool clear) {
   return e;
 }
 
+unsigned long long *device_status_word() {
+  void *p = nullptr;
+  return cudaGetSymbolAddress(&p, g_device_status) == cudaSuccess ? static_cast<unsigned long long *>(p) : nullptr;
+}
+
 namespace {
 thread_local char tls_detail[256] = "";
 }
