@@ -18,6 +18,7 @@ on a bounded sample of the same workload and extrapolates to the full size.
 """
 import argparse
 import json
+import math
 import os
 import sys
 import threading
@@ -408,6 +409,80 @@ def run_ours(args, torch):
             nbytes = e * Bl * M * cols
             per_kernel[name] = {"us": round(us, 2), "alg_MB": round(nbytes / 1e6, 1), "GBps": round(nbytes / us / 1e3, 1)}
 
+        # ---- the attention block the two operators are written for: window fwd -> scale, mask, softmax -> unwindow
+        # fwd, and its backward, with the band softmax of this library between the operators (7 launches).  Reported
+        # beside the headline (which stays the reference's own four calls), with the same block using torch ops for
+        # the softmax as the reference's users compose it.
+        block = None
+        if Bl > 0 and (args.block == "on" or (args.block == "auto" and args.workload == "c5")):
+            from window_matmul import softmax as sm_
+
+            scale = 1.0 / math.sqrt(N)
+
+            def block_step():
+                impl.band_nt(qd, ktd, w, out=a)
+                sm_.band_softmax(a, scale, True, out=a)                       # probabilities, in place
+                impl.band_n(a, vd, w, out=o)
+                impl.unwindow_matmul_backward(a, vd, w, god, out=(ga, gv))    # grad_P, grad_V
+                sm_.band_softmax_backward(a, ga, scale, True, out=ga)         # grad_scores, in place
+                impl.window_matmul_backward(qd, kd, w, ga, out=(gq, gkt))
+
+            def timed(fn, reps):
+                fn()
+                stream.synchronize()
+                g = None
+                if not args.no_graph:
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=stream):
+                        for _ in range(reps):
+                            fn()
+                    stream.synchronize()
+                t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                t0.record(stream)
+                if g is not None:
+                    g.replay()
+                else:
+                    for _ in range(reps):
+                        fn()
+                t1.record(stream)
+                stream.synchronize()
+                return t0.elapsed_time(t1) * 1e3 / reps
+
+            block_us = timed(block_step, 5)
+            sm_f = timed(lambda: sm_.band_softmax(a, scale, True, out=ga), 5)
+            sm_b = timed(lambda: sm_.band_softmax_backward(a, ga, scale, True, out=ga), 5)
+            band_bytes = e * Bl * M * W
+            ii = torch.arange(M, device=dev)[:, None]
+            jj = torch.arange(W, device=dev)[None, :]
+            outside = ((ii + jj - w) < 0) | ((ii + jj - w) >= M)
+            a_req = a.detach().clone().requires_grad_()
+
+            def torch_softmax_fwd_bwd():
+                pr = torch.softmax((a_req * scale).masked_fill(outside, float("-inf")), dim=-1)
+                pr.backward(ga)
+                a_req.grad = None
+
+            torch_us = timed(torch_softmax_fwd_bwd, 2) if args.no_graph else None
+            if torch_us is None:   # torch's autograd ops are timed from the stream, not from a graph
+                torch_softmax_fwd_bwd()
+                stream.synchronize()
+                t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                t0.record(stream)
+                for _ in range(3):
+                    torch_softmax_fwd_bwd()
+                t1.record(stream)
+                stream.synchronize()
+                torch_us = t0.elapsed_time(t1) * 1e3 / 3
+            del a_req
+            block_bytes = e * Bl * M * (11 * N + 10 * W)
+            block = {
+                "us": round(block_us, 1), "launches": 7, "alg_MB": round(block_bytes / 1e6, 1),
+                "GBps": round(block_bytes / block_us / 1e3, 1),
+                "softmax_fwd": {"us": round(sm_f, 1), "GBps": round(2 * band_bytes / sm_f / 1e3, 1)},
+                "softmax_bwd": {"us": round(sm_b, 1), "GBps": round(3 * band_bytes / sm_b / 1e3, 1)},
+                "torch_softmax_fwd_bwd_us": round(torch_us, 1),
+            }
+
         # ---- end to end through the public API, host buffers, copies inside the timed region ----
         e2e_steps = max(3, min(args.steps, 20))
         outs_host = [torch.empty(Bl, M, N, dtype=dtype).pin_memory() for _ in range(4)]
@@ -486,8 +561,9 @@ def run_ours(args, torch):
                 "traffic": traffic,
             },
             "per_kernel": per_kernel,
+            "attention_block": block,
             "e2e": {
-                "value": e2e_ms * 1e3, "unit": "us", "h2d_bytes_per_step": 4 * Bl * M * N * e * world,
+                "value": e2e_ms * 1e3 if run_e2e else None, "unit": "us", "h2d_bytes_per_step": 4 * Bl * M * N * e * world,
                 "d2h_bytes_per_step": 4 * Bl * M * N * e * world, "steps": e2e_steps,
             },
             "gpu_launches": int(launches),
@@ -622,6 +698,8 @@ def main():
                     help="multi-GPU partitioning: batch entries (default) or sequence rows with halo exchange (default for c4)")
     ap.add_argument("--e2e-chunks", type=int, default=8, help="batch chunks of the host-buffer leg")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--block", default="auto", choices=["auto", "on", "off"],
+                    help="also time the attention block with the band softmax between the operators (auto: config 5)")
     args = ap.parse_args()
     import torch
 

@@ -178,3 +178,52 @@ def test_config5_attention_block_bf16_vs_fp32(wm):
     ref = block(torch.float32)
     for name, x, y in zip(("o", "gq", "gk", "gv"), lo, ref):
         H.assert_lowp_close(x, y.cpu().numpy(), name, rel=1e-1)
+
+
+def test_config5_attention_block_with_band_softmax(wm):
+    """The same block with this library's band softmax between the operators instead of the torch ops: on identical
+    bf16 scores its probabilities and score gradients match torch's fp32 softmax of the masked, scaled scores at the
+    16-bit bound, and the whole fused block (bf16) stays within the bound of the all-fp32 torch-composed block."""
+    import window_matmul as pkg
+    from window_matmul import softmax as sm
+
+    B, M, Nn, w = 2, 16384, 64, 384
+    q, kt, v, go = _seeded(B, M, Nn, torch.float32, 5, dist="normal")
+    mask = torch.from_numpy(H.out_of_sequence_mask(M, w)).cuda()
+    bf = torch.bfloat16
+    scale = 1.0 / math.sqrt(Nn)
+
+    a = wm.window_matmul_forward(q.to(bf).cuda(), kt.to(bf).cuda().transpose(-1, -2), w)
+    s = (a.float() * scale).masked_fill(mask, float("-inf")).requires_grad_(True)
+    pf = torch.softmax(s, dim=-1)
+    p = sm.band_softmax(a, scale, True)
+    assert (p[:, mask] == 0).all()
+    H.assert_lowp_close(p, pf.detach().cpu().numpy(), "probabilities")
+    gp = torch.randn(p.shape, device="cuda", generator=torch.Generator(device="cuda").manual_seed(1)).to(bf)
+    (gs_ref,) = torch.autograd.grad(pf, s, gp.float())
+    # backward from the same (bf16) probabilities the kernel saved
+    pb = p.float().requires_grad_(True)
+    gs = sm.band_softmax_backward(p, gp, scale, True)
+    assert (gs[:, mask] == 0).all()
+    H.assert_lowp_close(gs, (gs_ref * scale).cpu().numpy(), "grad_scores", rel=2e-2)
+    del a, s, pf, p, gp, gs, gs_ref, pb
+
+    def fused_block(dtype):
+        qd, ktd, vd = (t.to(dtype).cuda().requires_grad_(True) for t in (q, kt, v))
+        pr = pkg.window_softmax(pkg.window_matmul(qd, ktd.transpose(-1, -2), w), scale, True)
+        out = pkg.unwindow_matmul(pr, vd, w)
+        out.backward(go.to(dtype).cuda())
+        return [t.detach().float() for t in (out, qd.grad, ktd.grad, vd.grad)]
+
+    def torch_block_fp32():
+        qd, ktd, vd = (t.cuda().requires_grad_(True) for t in (q, kt, v))
+        sc = (pkg.window_matmul(qd, ktd.transpose(-1, -2), w) * scale).masked_fill(mask, float("-inf"))
+        out = pkg.unwindow_matmul(torch.softmax(sc, dim=-1), vd, w)
+        out.backward(go.cuda())
+        return [t.detach() for t in (out, qd.grad, ktd.grad, vd.grad)]
+
+    ref = torch_block_fp32()
+    for name, x, y in zip(("o", "gq", "gk", "gv"), fused_block(torch.float32), ref):
+        H.assert_lowp_close(x, y.cpu().numpy(), name + " fp32", rel=1e-4)
+    for name, x, y in zip(("o", "gq", "gk", "gv"), fused_block(bf), ref):
+        H.assert_lowp_close(x, y.cpu().numpy(), name + " bf16", rel=1e-1)
