@@ -62,6 +62,37 @@ __device__ __forceinline__ void cp_async16(void *dst, const void *src, bool vali
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr(dst)), "l"(src), "r"(valid ? 16 : 0) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// untiled bulk copy shared -> global (both 16-byte aligned, size a multiple of 16 bytes), tracked by bulk groups
+__device__ __forceinline__ void bulk_store(void *dst, const void *src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(smem_addr(src)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// two floats -> two 16-bit values in one word (first in the low half)
+template <bool BF16> __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
+  if (BF16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+  }
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t *>(&v);
+}
+
+// The consecutive tiles a CTA owns, as (batch, tile in batch) of the first one and a count.
+struct TileRange {
+  int b, tb, count;
+  __device__ TileRange(int total, int per_batch) {
+    const int per = total / (int)gridDim.x, rem = total % (int)gridDim.x;
+    const int first = (int)blockIdx.x * per + min((int)blockIdx.x, rem);
+    count = per + ((int)blockIdx.x < rem ? 1 : 0);
+    b = first / per_batch;
+    tb = first % per_batch;
+  }
+};
+
 template <int KEEP> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(KEEP) : "memory"); }
 
 // Rows [row0, row0 + nrows) of a (batch, rows, N) operand with unit column stride -> shared memory with
@@ -128,24 +159,27 @@ template <bool BF16, int N, int NT_MAX> __global__ void __launch_bounds__(SM_THR
   const int nt_count = (16 + 2 * p.w + 7) / 8;
 
   // inputs of a tile -> stage buffer, asynchronously
-  auto prefetch = [&](int tile, int stage) {
-    const int b = tile / p.tiles_per_batch, r0 = (tile % p.tiles_per_batch) * SM_ROWS;
+  auto prefetch = [&](int b, int r0, int stage) {
     uint8_t *xs = smem + stage * p.in_bytes, *ys = xs + L::TILE_BYTES;
     load_rows<N, L::PITCH>(xs, p.a, p.a_sb, p.a_sr, b, r0, SM_ROWS, 0, p.M);
     load_rows<N, L::PITCH>(ys, p.b, p.b_sb, p.b_sr, b, r0 - p.w + p.off, (slab + 7) & ~7, p.lo, p.hi);
   };
 
-  int it = 0;
-  if ((int)blockIdx.x < p.total_tiles) prefetch(blockIdx.x, 0);
+  // this CTA's tiles are consecutive: (batch, tile-in-batch) advance without a division per tile
+  TileRange tr(p.total_tiles, p.tiles_per_batch);
+  int nb = tr.b, ntb = tr.tb;   // the tile being prefetched
+  if (tr.count > 0) prefetch(nb, ntb * SM_ROWS, 0);
   cp_async_commit();
-  for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++it) {
+  for (int it = 0; it < tr.count; ++it) {
     const int stage = it & 1;
-    if (tile + (int)gridDim.x < p.total_tiles) prefetch(tile + gridDim.x, stage ^ 1);
+    const int b = nb, r0 = ntb * SM_ROWS;
+    if (++ntb == p.tiles_per_batch) { ntb = 0; ++nb; }
+    if (it + 1 < tr.count) prefetch(nb, ntb * SM_ROWS, stage ^ 1);
     cp_async_commit();
     cp_async_wait<1>();  // this tile's inputs have landed (the next tile's may still be in flight)
-    __syncthreads();     // ... for every thread; also: the previous tile's image has been written out
+    if (threadIdx.x == 0) bulk_wait_read0();  // the previous tile's image has left shared memory
+    __syncthreads();     // ... for every thread
 
-    const int b = tile / p.tiles_per_batch, r0 = (tile % p.tiles_per_batch) * SM_ROWS;
     const int vr = min(SM_ROWS, p.M - r0), p0 = r0 - p.w + p.off;  // slab row s <-> position p0 + s
     const uint8_t *xs = smem + stage * p.in_bytes, *ys = xs + L::TILE_BYTES;
     uint16_t *out = p.o + ((int64_t)b * p.M + r0) * W;
@@ -175,28 +209,61 @@ template <bool BF16, int N, int NT_MAX> __global__ void __launch_bounds__(SM_THR
     }
     // scatter into the packed image: dense (row rl, slab column col) -> band index j = col - rl
     const bool edge = vr < SM_ROWS || p0 < p.lo || p0 + slab > p.hi;
+    if (!edge) {
+      // interior tile: element (q, nt, e) of this lane sits at rowp[q] + 8nt + e and has j = jb[q] + 8nt + e
+      uint16_t *rowp[2];
+      int jb[2];
 #pragma unroll
-    for (int nt = 0; nt < NT_MAX; nt++) {
-      if (nt < nt_count) {
+      for (int q = 0; q < 2; q++) {
+        const int rl = g + 8 * q;
+        jb[q] = 2 * t - rl;
+        rowp[q] = im + (warp * 16 + rl) * W + jb[q];
+      }
 #pragma unroll
-        for (int c = 0; c < 4; c++) {
-          const int rl = g + 8 * (c >> 1), col = nt * 8 + 2 * t + (c & 1);
-          const int j = col - rl;
-          bool ok = j >= 0 && j < W;
-          float val = acc[nt][c];
-          if (edge) {
+      for (int nt = 0; nt < NT_MAX; nt++) {
+        if (nt < nt_count) {
+#pragma unroll
+          for (int q = 0; q < 2; q++) {
+            const uint32_t pr = pack16<BF16>(acc[nt][2 * q], acc[nt][2 * q + 1]);
+            if ((unsigned)(jb[q] + nt * 8) < (unsigned)W) rowp[q][nt * 8] = (uint16_t)pr;
+            if ((unsigned)(jb[q] + nt * 8 + 1) < (unsigned)W) rowp[q][nt * 8 + 1] = (uint16_t)(pr >> 16);
+          }
+        }
+      }
+    } else {
+#pragma unroll
+      for (int nt = 0; nt < NT_MAX; nt++) {
+        if (nt < nt_count) {
+#pragma unroll
+          for (int c = 0; c < 4; c++) {
+            const int rl = g + 8 * (c >> 1), col = nt * 8 + 2 * t + (c & 1);
+            const int j = col - rl;
+            bool ok = j >= 0 && j < W;
+            float val = acc[nt][c];
             const int pos = p0 + warp * 16 + col;
             ok = ok && warp * 16 + rl < vr;
             if (pos < p.lo || pos >= p.hi) val = 0.f;
+            if (ok) im[(warp * 16 + rl) * W + j] = to16<BF16>(val);
           }
-          if (ok) im[(warp * 16 + rl) * W + j] = to16<BF16>(val);
         }
       }
     }
+    // a full tile whose destination is 16-byte aligned leaves with one bulk copy (128 rows of 2w+1 16-bit elements are
+    // a multiple of 16 bytes); ragged or unaligned tiles are copied out by all threads
+    const bool bulk_out = vr == SM_ROWS && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+    if (bulk_out) fence_async_smem();
     __syncthreads();
-    copy_span_out(out, im, (int64_t)vr * W);
+    if (bulk_out) {
+      if (threadIdx.x == 0) {
+        bulk_store(out, im, (uint32_t)(SM_ROWS * W * 2));
+        bulk_commit_group();
+      }
+    } else {
+      copy_span_out(out, im, (int64_t)vr * W);
+    }
   }
   cp_async_wait<0>();
+  if (threadIdx.x == 0) bulk_wait_all0();
 }
 
 // ---------------------------------------------------------------------------------------------------
