@@ -7,8 +7,10 @@
 // 16-byte accesses, each HBM byte once.  The arithmetic is done per warp on 16 rows with warp-level
 // m16n8k16 MMAs (fp32 accumulation) fed from shared memory: band_nt builds 16 x (16 + 2w) dense products
 // and scatters them into the packed band image; band_n / band_t gather the un-skewed band fragments from
-// the packed image.  No mbarriers, no waits on other CTAs: only __syncthreads.
+// the packed image.  Whole packed band tiles move with one untiled bulk copy where alignment allows (completion on an
+// mbarrier with a bounded wait); everything else is cp.async and __syncthreads.  No waits on other CTAs.
 #include "wmm_common.cuh"
+#include "wmm_ptx.cuh"
 
 namespace wmm {
 
@@ -25,6 +27,7 @@ struct SmallParams {
   int64_t a_sb, a_sr, b_sb, b_sr, o_sb, o_sr;
   int B, M, Mo, w, off, lo, hi, tiles_per_batch;
   int total_tiles;
+  unsigned long long *status;  // device status word (bit 3: a small-window kernel gave up on a bounded wait)
   int in_bytes;    // bytes of one input stage
   int slab_bytes;  // bytes of the slab inside an input stage
 };
@@ -270,22 +273,29 @@ template <bool BF16, int N, int NT_MAX> __global__ void __launch_bounds__(SM_THR
 // band_n (TR = false): Out[i, :] = sum_j Band[i, j] Y[i + j - w + off, :]          tile = 128 band rows
 // band_t (TR = true):  Out[p, :] = sum_i Band[i, p - off - i + w] X[i, :]          tile = 128 positions
 // ---------------------------------------------------------------------------------------------------
-template <bool BF16, int N, bool TR> __global__ void __launch_bounds__(SM_THREADS) band_mm_small_kernel(const SmallParams p) {
+template <bool BF16, int N, bool TR, int KS_MAX> __global__ void __launch_bounds__(SM_THREADS, N <= 64 ? 4 : 2) band_mm_small_kernel(const SmallParams p) {
   using L = SmallLayout<N>;
   extern __shared__ __align__(16) uint8_t smem[];
   uint8_t *os = smem + 2 * p.in_bytes;  // output staging
+  __shared__ __align__(8) uint64_t img_full[2];   // completion of a stage's bulk-loaded band image
+  __shared__ int abort_flag;
   const int W = 2 * p.w + 1;
   const int slab = SM_ROWS + 2 * p.w;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int ksteps = (16 + 2 * p.w + 15) / 16;
   const int out_rows = TR ? p.Mo : p.M;
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(smem_addr(&img_full[0]), 1);
+    ptx::mbar_init(smem_addr(&img_full[1]), 1);
+    abort_flag = 0;
+    ptx::fence_mbar_init();
+  }
+  __syncthreads();
 
   // Per tile: t0 = first band row (band_n) / position (band_t).  Slab row s of the other operand is
   // position t0 - w + off + s (band_n) or band row t0 - off - w + s (band_t).  The image holds band rows
   // [t0, t0 + 128) (band_n) or [s0, s0 + 128 + 2w) (band_t), clipped to [0, M).
-  auto geometry = [&](int tile, int &b, int &t0, int &s0, int &ilo, int &ihi) {
-    b = tile / p.tiles_per_batch;
-    t0 = (tile % p.tiles_per_batch) * SM_ROWS;
+  auto geometry = [&](int t0, int &s0, int &ilo, int &ihi) {
     s0 = TR ? t0 - p.off - p.w : t0 - p.w + p.off;
     const int img_row0 = TR ? s0 : t0;
     ilo = max(img_row0, 0);
@@ -295,9 +305,13 @@ template <bool BF16, int N, bool TR> __global__ void __launch_bounds__(SM_THREAD
     uint16_t *img = reinterpret_cast<uint16_t *>(smem + stage * p.in_bytes + p.slab_bytes);
     return img + ((reinterpret_cast<uintptr_t>(band) & 15) >> 1);  // same 16-byte phase as the source
   };
-  auto prefetch = [&](int tile, int stage) {
-    int b, t0, s0, ilo, ihi;
-    geometry(tile, b, t0, s0, ilo, ihi);
+  // the image of a tile moves with one bulk copy when its source is 16-byte aligned and a multiple of 16 bytes long
+  auto image_bulk = [&](const uint16_t *band, int rows) -> bool {
+    return (reinterpret_cast<uintptr_t>(band) & 15) == 0 && ((rows * W * 2) & 15) == 0;
+  };
+  auto prefetch = [&](int b, int t0, int stage) {
+    int s0, ilo, ihi;
+    geometry(t0, s0, ilo, ihi);
     uint8_t *ys = smem + stage * p.in_bytes;
     if (!TR)
       load_rows<N, L::PITCH>(ys, p.b, p.b_sb, p.b_sr, b, s0, (slab + 15) & ~15, p.lo, p.hi);
@@ -305,35 +319,62 @@ template <bool BF16, int N, bool TR> __global__ void __launch_bounds__(SM_THREAD
       load_rows<N, L::PITCH>(ys, p.b, p.b_sb, p.b_sr, b, s0, (slab + 15) & ~15, 0, p.M);
     if (ihi > ilo) {
       const uint16_t *band = p.a + ((int64_t)b * p.M + ilo) * W;
-      copy_span_in(image_of(stage, band), band, (int64_t)(ihi - ilo) * W);
+      if (image_bulk(band, ihi - ilo)) {
+        if (threadIdx.x == 0) {
+          const uint32_t bytes = (uint32_t)((ihi - ilo) * W * 2);
+          ptx::mbar_expect_tx(smem_addr(&img_full[stage]), bytes);
+          ptx::bulk_load_1d(smem_addr(image_of(stage, band)), band, bytes, smem_addr(&img_full[stage]));
+        }
+      } else {
+        copy_span_in(image_of(stage, band), band, (int64_t)(ihi - ilo) * W);
+      }
     }
   };
 
-  int it = 0;
-  if ((int)blockIdx.x < p.total_tiles) prefetch(blockIdx.x, 0);
+  TileRange tr(p.total_tiles, p.tiles_per_batch);
+  int nb = tr.b, ntb = tr.tb;
+  uint32_t full_phase[2] = {0u, 0u};
+  bool aborted = false;
+  if (tr.count > 0) prefetch(nb, ntb * SM_ROWS, 0);
   cp_async_commit();
-  for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++it) {
+  for (int it = 0; it < tr.count; ++it) {
     const int stage = it & 1;
-    if (tile + (int)gridDim.x < p.total_tiles) prefetch(tile + gridDim.x, stage ^ 1);
+    const int b = nb, t0 = ntb * SM_ROWS;
+    if (++ntb == p.tiles_per_batch) { ntb = 0; ++nb; }
+    if (it + 1 < tr.count) prefetch(nb, ntb * SM_ROWS, stage ^ 1);
     cp_async_commit();
     cp_async_wait<1>();
-    __syncthreads();  // this tile's inputs are visible to all; the previous tile's output staging is drained
 
-    int b, t0, s0, ilo, ihi;
-    geometry(tile, b, t0, s0, ilo, ihi);
+    int s0, ilo, ihi;
+    geometry(t0, s0, ilo, ihi);
+    const uint16_t *band = p.a + ((int64_t)b * p.M + ilo) * W;
+    if (ihi > ilo && image_bulk(band, ihi - ilo)) {
+      if (!ptx::mbar_wait(smem_addr(&img_full[stage]), full_phase[stage], &abort_flag)) aborted = true;
+      full_phase[stage] ^= 1u;
+    }
+    __syncthreads();  // this tile's inputs are visible to all; the previous tile's output staging is drained
+    if (abort_flag) { aborted = true; break; }
+
     const uint8_t *ys = smem + stage * p.in_bytes;
     // the image starts at band row ilo; offsets below are relative to the unclipped first row
     const int img_row0 = TR ? s0 : t0;
-    const uint16_t *im = image_of(stage, p.a + ((int64_t)b * p.M + ilo) * W) - (ilo - img_row0) * W;
+    const uint16_t *im = image_of(stage, band) - (ilo - img_row0) * W;
     const bool edge = ilo != img_row0 || ihi != img_row0 + (TR ? slab : SM_ROWS) ||
                       (TR ? (t0 < p.lo || t0 + SM_ROWS > p.hi) : (s0 < p.lo || s0 + slab > p.hi));
     // image offset of dense element (ml, kc) = abase[ml] + kc (band_n) or abase[ml] + kc * 2w (band_t)
     int abase[2];
+    // interior tiles: element with compile-time offset C = 16 ks + 8 (r >> 1) + e sits at ptr[q][C] (band_n) or
+    // ptr[q][C * 2w] (band_t) and is inside the band iff (unsigned)(jd[q] + C) < W resp. (unsigned)(jd[q] - C) < W
+    const uint16_t *ptr[2];
+    int jd[2];
 #pragma unroll
     for (int q = 0; q < 2; q++) {
       const int ml = g + 8 * q;
       abase[q] = TR ? warp * 16 * W + 2 * p.w + ml : (warp * 16 + ml) * W - ml;
+      jd[q] = TR ? ml - 2 * t + 2 * p.w : 2 * t - ml;
+      ptr[q] = im + abase[q] + (TR ? 2 * t * (W - 1) : 2 * t);
     }
+    const int kstride = W - 1;
 
     float acc[N / 8][4];
 #pragma unroll
@@ -342,37 +383,57 @@ template <bool BF16, int N, bool TR> __global__ void __launch_bounds__(SM_THREAD
       for (int c = 0; c < 4; c++) acc[nt][c] = 0.f;
     // B fragments: rows (reduction index) of the slab starting at the warp's first one, hidden columns in n
     const uint32_t ybase = smem_addr(ys) + (warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * L::PITCH + 16 * (lane >> 4);
-    for (int ks = 0; ks < ksteps; ks++) {
-      // A fragment gathered from the packed image.  Dense element (m = ml, k = kc) with kc counted from
-      // the warp's first slab row:  band_n: row i = t0 + 16 warp + ml, j = kc - ml
-      //                             band_t: position = t0 + 16 warp + ml, row i = s0 + 16 warp + kc, j = ml - kc + 2w
-      uint32_t a[4];
 #pragma unroll
-      for (int r = 0; r < 4; r++) {
-        const int ml = g + 8 * (r & 1), kc0 = ks * 16 + 2 * t + 8 * (r >> 1);
-        uint32_t v = 0;
+    for (int ks = 0; ks < KS_MAX; ks++) {
+      if (ks < ksteps) {
+        // A fragment gathered from the packed image.  Dense element (m = ml, k = kc) with kc counted from
+        // the warp's first slab row:  band_n: row i = t0 + 16 warp + ml, j = kc - ml
+        //                             band_t: position = t0 + 16 warp + ml, row i = s0 + 16 warp + kc, j = ml - kc + 2w
+        uint32_t a[4];
+        if (!edge) {
 #pragma unroll
-        for (int e = 0; e < 2; e++) {
-          const int kc = kc0 + e;
-          // band index and image offset: band_n j = kc - ml, offset row*W + j; band_t j = ml - kc + 2w, row kc
-          const int j = TR ? ml - kc + 2 * p.w : kc - ml;
-          const int idx = TR ? abase[r & 1] + kc * (W - 1) : abase[r & 1] + kc;
-          bool ok = j >= 0 && j < W;
-          if (edge) {  // ragged or sequence-end tile: also check the band row and the position
-            const int i = TR ? s0 + warp * 16 + kc : t0 + warp * 16 + ml;
-            const int pos = TR ? t0 + warp * 16 + ml : s0 + warp * 16 + kc;
-            ok = ok && i >= ilo && i < ihi && pos >= p.lo && pos < p.hi;
+          for (int r = 0; r < 4; r++) {
+            const int q = r & 1;
+            uint32_t v = 0;
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+              const int C = ks * 16 + 8 * (r >> 1) + e;
+              if (!TR) {
+                if ((unsigned)(jd[q] + C) < (unsigned)W) v |= (uint32_t)ptr[q][C] << (16 * e);
+              } else {
+                if ((unsigned)(jd[q] - C) < (unsigned)W) v |= (uint32_t)ptr[q][C * kstride] << (16 * e);
+              }
+            }
+            a[r] = v;
           }
-          if (ok) v |= (uint32_t)im[idx] << (16 * e);
-        }
-        a[r] = v;
-      }
+        } else {
 #pragma unroll
-      for (int np = 0; np < N / 16; np++) {  // two n-tiles (16 hidden columns) per ldmatrix
-        uint32_t bb[4];
-        ldmatrix_x4_trans(bb, ybase + ks * 16 * L::PITCH + np * 32);
-        mma_16816<BF16>(acc[2 * np], a, bb[0], bb[1]);
-        mma_16816<BF16>(acc[2 * np + 1], a, bb[2], bb[3]);
+          for (int r = 0; r < 4; r++) {
+            const int ml = g + 8 * (r & 1), kc0 = ks * 16 + 2 * t + 8 * (r >> 1);
+            uint32_t v = 0;
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+              const int kc = kc0 + e;
+              // band index and image offset: band_n j = kc - ml, offset row*W + j; band_t j = ml - kc + 2w, row kc
+              const int j = TR ? ml - kc + 2 * p.w : kc - ml;
+              const int idx = TR ? abase[r & 1] + kc * (W - 1) : abase[r & 1] + kc;
+              bool ok = j >= 0 && j < W;
+              // ragged or sequence-end tile: also check the band row and the position
+              const int i = TR ? s0 + warp * 16 + kc : t0 + warp * 16 + ml;
+              const int pos = TR ? t0 + warp * 16 + ml : s0 + warp * 16 + kc;
+              ok = ok && i >= ilo && i < ihi && pos >= p.lo && pos < p.hi;
+              if (ok) v |= (uint32_t)im[idx] << (16 * e);
+            }
+            a[r] = v;
+          }
+        }
+#pragma unroll
+        for (int np = 0; np < N / 16; np++) {  // two n-tiles (16 hidden columns) per ldmatrix
+          uint32_t bb[4];
+          ldmatrix_x4_trans(bb, ybase + ks * 16 * L::PITCH + np * 32);
+          mma_16816<BF16>(acc[2 * np], a, bb[0], bb[1]);
+          mma_16816<BF16>(acc[2 * np + 1], a, bb[2], bb[3]);
+        }
       }
     }
     // stage the 128 x N output tile, then write whole rows with 16-byte stores
@@ -381,18 +442,25 @@ template <bool BF16, int N, bool TR> __global__ void __launch_bounds__(SM_THREAD
 #pragma unroll
       for (int c = 0; c < 4; c += 2) {
         const int row = warp * 16 + g + 4 * c, col = nt * 8 + 2 * t;
-        const uint32_t v = (uint32_t)to16<BF16>(acc[nt][c]) | ((uint32_t)to16<BF16>(acc[nt][c + 1]) << 16);
-        *reinterpret_cast<uint32_t *>(os + row * L::PITCH + col * 2) = v;
+        *reinterpret_cast<uint32_t *>(os + row * L::PITCH + col * 2) = pack16<BF16>(acc[nt][c], acc[nt][c + 1]);
       }
     __syncthreads();
     constexpr int PIECES = N / 8;
-    for (int e = threadIdx.x; e < SM_ROWS * PIECES; e += SM_THREADS) {
+    uint16_t *obase = p.o + b * p.o_sb + (int64_t)t0 * p.o_sr;
+    const int vrows = min(SM_ROWS, out_rows - t0);
+    for (int e = threadIdx.x; e < vrows * PIECES; e += SM_THREADS) {
       const int r = e / PIECES, pc = e % PIECES;
-      if (t0 + r < out_rows)
-        *reinterpret_cast<uint4 *>(p.o + b * p.o_sb + (int64_t)(t0 + r) * p.o_sr + pc * 8) = *reinterpret_cast<const uint4 *>(os + r * L::PITCH + pc * 16);
+      *reinterpret_cast<uint4 *>(obase + (int64_t)r * p.o_sr + pc * 8) = *reinterpret_cast<const uint4 *>(os + r * L::PITCH + pc * 16);
     }
   }
   cp_async_wait<0>();
+  if (aborted || abort_flag) {
+    __syncthreads();
+    if (threadIdx.x == 0 && p.status) atomicOr(p.status, 8ull);
+    // give a bulk copy that may still be in flight time to land before shared memory goes away
+    const uint64_t t_begin = ptx::globaltimer_ns();
+    while (ptx::globaltimer_ns() - t_begin < 2000000ull) __nanosleep(1000);
+  }
 }
 
 // Persistent grid: as many CTAs as fit on the device at this shared-memory size (each loops over tiles).
@@ -423,8 +491,15 @@ template <bool BF16, int N> cudaError_t launch_small_n(Primitive prim, SmallPara
     return launch(band_nt_small_kernel<BF16, N, 10>, k, L::nt_bytes(k.w), stream);
   }
   k.in_bytes = L::mm_in(k.w);
-  if (prim == BAND_N) return launch(band_mm_small_kernel<BF16, N, false>, k, L::mm_bytes(k.w), stream);
-  return launch(band_mm_small_kernel<BF16, N, true>, k, L::mm_bytes(k.w), stream);
+  const int smem = L::mm_bytes(k.w);
+  if (prim == BAND_N) {
+    if (k.w <= 8) return launch(band_mm_small_kernel<BF16, N, false, 2>, k, smem, stream);
+    if (k.w <= 16) return launch(band_mm_small_kernel<BF16, N, false, 3>, k, smem, stream);
+    return launch(band_mm_small_kernel<BF16, N, false, 5>, k, smem, stream);
+  }
+  if (k.w <= 8) return launch(band_mm_small_kernel<BF16, N, true, 2>, k, smem, stream);
+  if (k.w <= 16) return launch(band_mm_small_kernel<BF16, N, true, 3>, k, smem, stream);
+  return launch(band_mm_small_kernel<BF16, N, true, 5>, k, smem, stream);
 }
 
 bool rows_ok(const void *data, int64_t sb, int64_t sr, int64_t sc, int batch) {
@@ -451,6 +526,7 @@ cudaError_t launch_small(Primitive prim, const Problem &p, cudaStream_t stream, 
   k.b = static_cast<const uint16_t *>(p.b);
   k.o = static_cast<uint16_t *>(p.o);
   k.a_sb = p.a_sb; k.a_sr = p.a_sr; k.b_sb = p.b_sb; k.b_sr = p.b_sr; k.o_sb = p.o_sb; k.o_sr = p.o_sr;
+  k.status = device_status_word();
   k.B = p.B; k.M = p.M; k.Mo = p.Mo; k.w = p.w; k.off = p.off; k.lo = p.lo; k.hi = p.hi;
   const int tile_rows = prim == BAND_T ? p.Mo : p.M;
   k.tiles_per_batch = (tile_rows + SM_ROWS - 1) / SM_ROWS;
