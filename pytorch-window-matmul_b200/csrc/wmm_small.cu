@@ -112,6 +112,17 @@ __device__ __forceinline__ void load_rows(uint8_t *dst, const uint16_t *src, int
   }
 }
 
+// The common case of load_rows: all nrows rows are in range and contiguous in global memory (row stride N), so 16-byte
+// piece e of the block goes from src + 8e elements to dst + 16e + 16 (e / pieces-per-row) bytes: no per-piece row
+// arithmetic, no range checks.
+template <int N>
+__device__ __forceinline__ void load_block(uint8_t *dst, const uint16_t *src, int nrows) {
+  constexpr int PIECES = N / 8;
+  const uint32_t d = smem_addr(dst);
+  for (int e = threadIdx.x; e < nrows * PIECES; e += SM_THREADS)
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d + e * 16 + (e / PIECES) * 16), "l"(src + e * 8) : "memory");
+}
+
 // nelem contiguous 16-bit elements between global memory and shared memory.  `sm` holds the span at the
 // same offset modulo 16 bytes as `gm`, so 16-byte accesses line up on both sides.  The body of the inbound
 // copy is asynchronous; the (rare) unaligned head and tail elements are copied through registers.
@@ -164,8 +175,15 @@ template <bool BF16, int N, int NT_MAX> __global__ void __launch_bounds__(SM_THR
   // inputs of a tile -> stage buffer, asynchronously
   auto prefetch = [&](int b, int r0, int stage) {
     uint8_t *xs = smem + stage * p.in_bytes, *ys = xs + L::TILE_BYTES;
-    load_rows<N, L::PITCH>(xs, p.a, p.a_sb, p.a_sr, b, r0, SM_ROWS, 0, p.M);
-    load_rows<N, L::PITCH>(ys, p.b, p.b_sb, p.b_sr, b, r0 - p.w + p.off, (slab + 7) & ~7, p.lo, p.hi);
+    const int yrows = (slab + 7) & ~7, y0 = r0 - p.w + p.off;
+    if (p.a_sr == N && r0 + SM_ROWS <= p.M)
+      load_block<N>(xs, p.a + b * p.a_sb + (int64_t)r0 * N, SM_ROWS);
+    else
+      load_rows<N, L::PITCH>(xs, p.a, p.a_sb, p.a_sr, b, r0, SM_ROWS, 0, p.M);
+    if (p.b_sr == N && y0 >= p.lo && y0 + yrows <= p.hi)
+      load_block<N>(ys, p.b + b * p.b_sb + (int64_t)y0 * N, yrows);
+    else
+      load_rows<N, L::PITCH>(ys, p.b, p.b_sb, p.b_sr, b, y0, yrows, p.lo, p.hi);
   };
 
   // this CTA's tiles are consecutive: (batch, tile-in-batch) advance without a division per tile
@@ -313,10 +331,11 @@ template <bool BF16, int N, bool TR, int KS_MAX> __global__ void __launch_bounds
     int s0, ilo, ihi;
     geometry(t0, s0, ilo, ihi);
     uint8_t *ys = smem + stage * p.in_bytes;
-    if (!TR)
-      load_rows<N, L::PITCH>(ys, p.b, p.b_sb, p.b_sr, b, s0, (slab + 15) & ~15, p.lo, p.hi);
+    const int yrows = (slab + 15) & ~15, vlo = TR ? 0 : p.lo, vhi = TR ? p.M : p.hi;
+    if (p.b_sr == N && s0 >= vlo && s0 + yrows <= vhi)
+      load_block<N>(ys, p.b + b * p.b_sb + (int64_t)s0 * N, yrows);
     else
-      load_rows<N, L::PITCH>(ys, p.b, p.b_sb, p.b_sr, b, s0, (slab + 15) & ~15, 0, p.M);
+      load_rows<N, L::PITCH>(ys, p.b, p.b_sb, p.b_sr, b, s0, yrows, vlo, vhi);
     if (ihi > ilo) {
       const uint16_t *band = p.a + ((int64_t)b * p.M + ilo) * W;
       if (image_bulk(band, ihi - ilo)) {
@@ -448,9 +467,14 @@ template <bool BF16, int N, bool TR, int KS_MAX> __global__ void __launch_bounds
     constexpr int PIECES = N / 8;
     uint16_t *obase = p.o + b * p.o_sb + (int64_t)t0 * p.o_sr;
     const int vrows = min(SM_ROWS, out_rows - t0);
-    for (int e = threadIdx.x; e < vrows * PIECES; e += SM_THREADS) {
-      const int r = e / PIECES, pc = e % PIECES;
-      *reinterpret_cast<uint4 *>(obase + (int64_t)r * p.o_sr + pc * 8) = *reinterpret_cast<const uint4 *>(os + r * L::PITCH + pc * 16);
+    if (p.o_sr == N) {  // contiguous output rows: piece e of the block
+      for (int e = threadIdx.x; e < vrows * PIECES; e += SM_THREADS)
+        *reinterpret_cast<uint4 *>(obase + e * 8) = *reinterpret_cast<const uint4 *>(os + e * 16 + (e / PIECES) * 16);
+    } else {
+      for (int e = threadIdx.x; e < vrows * PIECES; e += SM_THREADS) {
+        const int r = e / PIECES, pc = e % PIECES;
+        *reinterpret_cast<uint4 *>(obase + (int64_t)r * p.o_sr + pc * 8) = *reinterpret_cast<const uint4 *>(os + r * L::PITCH + pc * 16);
+      }
     }
   }
   cp_async_wait<0>();
