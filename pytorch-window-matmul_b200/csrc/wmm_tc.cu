@@ -100,6 +100,7 @@ template <bool BF16> __device__ __forceinline__ uint16_t pack1(uint32_t bits) {
 #include "wmm_tc_nt.cuh"
 
 #include "wmm_tc_mm.cuh"
+#include "wmm_tc_sweep.cuh"
 
 // ---------------------------------------------------------------------------------------------------
 // host side
@@ -310,6 +311,41 @@ template <int MODE> cudaError_t launch_mm_any(const Problem &p, const Problem *p
   return launch_mm_n<MODE, false>(p, pt, stream);
 }
 
+// grad_Q and grad_K^T of window_matmul in one sweep over grad_A (see wmm_tc_sweep.cuh for the conditions).
+bool sweep_eligible(const Problem &pn, const Problem &pt) {
+  if (pn.w < 128 || (pn.w % 128) != 0) return false;
+  const int D = pn.w / 128;
+  if (2 * D + 2 > SweepSmem<32>::MAX_SLOTS || (2 * D + 4) * pn.N > 512) return false;
+  if (pn.lo != 0 || pn.hi != pn.M || y_position_major(pn)) return false;
+  return true;
+}
+
+template <bool BF16, int NH> cudaError_t launch_sweep(const Problem &pn, const Problem &pt, cudaStream_t stream) {
+  using S = SweepSmem<NH>;
+  using OT = KMajorTile<NH>;
+  SweepParams k;
+  k.B = pn.B; k.M = pn.M; k.w = pn.w; k.D = pn.w / 128;
+  k.T = (pn.M + TILE - 1) / TILE;
+  k.total_rows = k.B * k.T;
+  auto kern = band_bwd_sweep_kernel<BF16, NH>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::ALLOC);
+  if (e != cudaSuccess) {
+    set_launch_detail("cudaFuncSetAttribute(band_bwd_sweep, %d bytes of shared memory)", S::ALLOC);
+    return e;
+  }
+  CUtensorMap mband, my, mx, mgq, mgk;
+  if (!make_band_map(&mband, BF16, pn.a, pn.M, pn.w, pn.B) ||
+      !make_operand_map(&my, BF16, pn.b, NH, pn.Mo, pn.B, pn.b_sr, pn.b_sb, OT::BOXK) ||
+      !make_operand_map(&mx, BF16, pt.b, NH, pt.M, pt.B, pt.b_sr, pt.b_sb, OT::BOXK) ||
+      !make_operand_map(&mgq, BF16, pn.o, NH, pn.M, pn.B, pn.o_sr, pn.o_sb, OT::BOXK) ||
+      !make_operand_map(&mgk, BF16, pt.o, NH, pt.Mo, pt.B, pt.o_sr, pt.o_sb, OT::BOXK))
+    return cudaErrorInvalidValue;
+  const int grid = persistent_grid(k.total_rows);
+  set_launch_detail("band_bwd_sweep launch, grid %d", grid);
+  kern<<<grid, SWP_THREADS, S::ALLOC, stream>>>(mband, my, mx, mgq, mgk, k);
+  return cudaGetLastError();
+}
+
 }  // namespace
 
 bool tensor_eligible(Primitive prim, const Problem &p) {
@@ -357,7 +393,14 @@ bool tensor_fused_pair_eligible(const Problem &pn, const Problem &pt) {
 }
 
 cudaError_t launch_tensor_fused_pair(const Problem &pn, const Problem &pt, cudaStream_t stream, int *launches) {
-  cudaError_t e = launch_mm_any<2>(pn, &pt, stream);
+  cudaError_t e;
+  if (sweep_eligible(pn, pt)) {
+    const bool bf16 = pn.dtype == WMM_BF16;
+    if (pn.N == 32) e = bf16 ? launch_sweep<true, 32>(pn, pt, stream) : launch_sweep<false, 32>(pn, pt, stream);
+    else e = bf16 ? launch_sweep<true, 64>(pn, pt, stream) : launch_sweep<false, 64>(pn, pt, stream);
+  } else {
+    e = launch_mm_any<2>(pn, &pt, stream);
+  }
   if (e == cudaSuccess && launches) ++*launches;
   return e;
 }

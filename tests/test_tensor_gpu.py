@@ -173,6 +173,36 @@ def test_window_backward_fused_tensor(wm, shape):
     H.assert_lowp_close(gk, want_gk, "grad_k %s" % (shape,))
 
 
+# windows of 128 and 256 with N <= 64 take the one-sweep backward kernel: runs of row tiles that start inside a sequence
+# (more row tiles than SMs), sequences shorter than the window, ragged last tiles, one and many sequences per CTA
+SWEEP_SHAPES = [(20, 2048, 64, 256), (3, 2048, 64, 256), (2, 1000, 64, 128), (5, 384, 32, 128), (1, 128, 64, 256),
+                (2, 256, 64, 256), (7, 640, 64, 256), (160, 128, 32, 128), (40, 520, 64, 128)]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", SWEEP_SHAPES)
+def test_window_backward_one_sweep(wm, shape, dtype):
+    """grad_Q and grad_K from the kernel that brings each box of grad_A into shared memory once.  The out-of-sequence
+    slots of grad_A hold NaN: the reference never reads them, so they must not reach either result."""
+    from window_matmul import _native as N
+
+    B, M, Nn, w = shape
+    d = _inputs(shape, dtype, seed=17)
+    want_gq, want_gk = H.oracle.window_matmul_backward(d["q"], np.ascontiguousarray(d["kt"].transpose(0, 2, 1)), w, d["g_band"])
+    g_band = d["g_band"].copy()
+    g_band[:, H.out_of_sequence_mask(M, w)] = np.nan
+    q, kt, gb = H.to_dev(d["q"], dtype), H.to_dev(d["kt"], dtype), H.to_dev(g_band, dtype)
+    gq = torch.full((B, M, Nn), float("nan"), dtype=dtype, device="cuda")
+    gkt = torch.full((B, M, Nn), float("nan"), dtype=dtype, device="cuda")
+    before = N.launch_count()
+    wm.window_matmul_backward(q, kt.transpose(-1, -2), w, gb, out=(gq, gkt))
+    assert N.launch_count() - before == 1
+    torch.cuda.synchronize()
+    assert N.device_status() == 0
+    H.assert_lowp_close(gq, want_gq, "grad_q %s" % (shape,))
+    H.assert_lowp_close(gkt, want_gk.transpose(0, 2, 1), "grad_k %s" % (shape,))
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("shape", SMALL_SHAPES)
 def test_small_window_family(wm, shape, dtype):
