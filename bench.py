@@ -41,7 +41,10 @@ WORKLOADS = {
 METRIC = "fwd+bwd window+unwindow us at B=96 M=4096 N=64 w=256"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, per band row, from the ncu capture summarised in
 # profiles/band_kernels_c2_b48_bf16.md (B=48: 196608 rows per launch).
-NCU_DRAM_BYTES_PER_ROW = {"c2": {"band_nt": 1008.8, "band_n+band_t": 1474.3, "band_n": 1245.0, "band_t": 1242.9}}
+# (bytes per band row, bytes per launch).  The window backward (one sweep over grad_A) re-reads a fixed number of boxes at
+# the start of every CTA's run: 59.7 MB per launch whatever the batch, on top of 1461.8 B per band row.
+NCU_DRAM_BYTES_PER_ROW = {"c2": {"band_nt": (1008.8, 0.0), "band_n+band_t": (1461.8, 59.7e6), "band_n": (1245.0, 0.0),
+                                 "band_t": (1242.9, 0.0)}}
 
 
 def algorithmic(B, M, N, w, e):
@@ -537,7 +540,7 @@ def run_ours(args, torch):
         if dom[0] and args.workload in NCU_DRAM_BYTES_PER_ROW:
             per_row = NCU_DRAM_BYTES_PER_ROW[args.workload].get(dom[0].split()[-1])
             if per_row:  # captured at B=48; traffic grows in proportion to the band rows of a launch
-                traffic = per_row * Bl * M
+                traffic = per_row[0] * Bl * M + per_row[1]
         line = {
             "metric": METRIC if args.workload == "c2" and not args.batch else "fwd+bwd window+unwindow us (%s)" % args.workload,
             "value": us_per_step, "unit": "us", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
