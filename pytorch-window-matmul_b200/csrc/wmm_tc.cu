@@ -333,16 +333,16 @@ template <bool BF16, int NH> cudaError_t launch_sweep(const Problem &pn, const P
     set_launch_detail("cudaFuncSetAttribute(band_bwd_sweep, %d bytes of shared memory)", S::ALLOC);
     return e;
   }
-  CUtensorMap mband, my, mx, mgq, mgk;
+  k.gq = static_cast<uint16_t *>(pn.o); k.gq_sb = pn.o_sb; k.gq_sr = pn.o_sr;
+  k.gk = static_cast<uint16_t *>(pt.o); k.gk_sb = pt.o_sb; k.gk_sr = pt.o_sr;
+  CUtensorMap mband, my, mx;
   if (!make_band_map(&mband, BF16, pn.a, pn.M, pn.w, pn.B) ||
       !make_operand_map(&my, BF16, pn.b, NH, pn.Mo, pn.B, pn.b_sr, pn.b_sb, OT::BOXK) ||
-      !make_operand_map(&mx, BF16, pt.b, NH, pt.M, pt.B, pt.b_sr, pt.b_sb, OT::BOXK) ||
-      !make_operand_map(&mgq, BF16, pn.o, NH, pn.M, pn.B, pn.o_sr, pn.o_sb, OT::BOXK) ||
-      !make_operand_map(&mgk, BF16, pt.o, NH, pt.Mo, pt.B, pt.o_sr, pt.o_sb, OT::BOXK))
+      !make_operand_map(&mx, BF16, pt.b, NH, pt.M, pt.B, pt.b_sr, pt.b_sb, OT::BOXK))
     return cudaErrorInvalidValue;
   const int grid = persistent_grid(k.total_rows);
   set_launch_detail("band_bwd_sweep launch, grid %d", grid);
-  kern<<<grid, SWP_THREADS, S::ALLOC, stream>>>(mband, my, mx, mgq, mgk, k);
+  kern<<<grid, SWP_THREADS, S::ALLOC, stream>>>(mband, my, mx, k);
   return cudaGetLastError();
 }
 

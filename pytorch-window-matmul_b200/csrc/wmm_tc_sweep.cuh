@@ -26,17 +26,19 @@ constexpr unsigned long long ST_SWEEP_TIMEOUT = 1ull << 4;
 struct SweepParams {
   int B, M, w, D, T;   // T = row tiles (= position tiles) per sequence
   int total_rows;      // B * T
+  // outputs (element strides; unit column stride): written straight from registers, a 2 NH-byte row per thread
+  uint16_t *gq, *gk;
+  int64_t gq_sb, gq_sr, gk_sb, gk_sr;
 };
 
 template <int NH> struct SweepSmem {
   using BT = KMajorTile<128>;
   using OT = KMajorTile<NH>;
-  static constexpr int STAGES = 3;
+  static constexpr int STAGES = 4;
   static constexpr int MAX_SLOTS = 6;   // column accumulators (2D + 2 <= 6)
   static constexpr int STAGE_BYTES = BT::BYTES + OT::BYTES;
   static constexpr int OFF_X = STAGES * STAGE_BYTES;   // two Q tiles
-  static constexpr int OFF_OUT = OFF_X + 2 * OT::BYTES;
-  static constexpr int OFF_BARS = OFF_OUT + OT::BYTES;
+  static constexpr int OFF_BARS = OFF_X + 2 * OT::BYTES;
   static constexpr int NBARS = 3 * STAGES + 8 + 2 * MAX_SLOTS;
   static constexpr int OFF_MISC = OFF_BARS + NBARS * 8;
   static constexpr int BYTES = OFF_MISC + 32;
@@ -86,8 +88,7 @@ __device__ __forceinline__ bool sweep_walk(const SweepParams &p, RowBegin row_be
 template <bool BF16, int NH>
 __global__ void __launch_bounds__(SWP_THREADS, 1)
 band_bwd_sweep_kernel(const __grid_constant__ CUtensorMap map_band, const __grid_constant__ CUtensorMap map_y,
-                      const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_gq,
-                      const __grid_constant__ CUtensorMap map_gk, const SweepParams p) {
+                      const __grid_constant__ CUtensorMap map_x, const SweepParams p) {
   using S = SweepSmem<NH>;
   using BT = typename S::BT;
   using OT = typename S::OT;
@@ -133,8 +134,6 @@ band_bwd_sweep_kernel(const __grid_constant__ CUtensorMap map_band, const __grid
     prefetch_tmap(&map_band);
     prefetch_tmap(&map_y);
     prefetch_tmap(&map_x);
-    prefetch_tmap(&map_gq);
-    prefetch_tmap(&map_gk);
   }
   if (warp == 1) {
     tmem_alloc(base + S::OFF_MISC, 512);
@@ -322,50 +321,38 @@ band_bwd_sweep_kernel(const __grid_constant__ CUtensorMap map_band, const __grid
         [&](int, int) { return true; }, [&](int, int) { return true; }, [&](bool) { return true; });
   } else {
     // ---------------- epilogue: thread <-> output row of the tile ----------------
+    // Each thread owns one output row of 2 NH bytes (a whole 128-byte line at NH = 64) and writes it from registers:
+    // no staging buffer, which is what leaves room for the fourth pipeline stage.
     const int quarter = warp & 3;
     const int rr = quarter * 32 + lane;
     const int epi_tid = threadIdx.x - 192;
-    const uint32_t stage = base + S::OFF_OUT;
     int nrow = 0;
     uint32_t col_bits = 0;
-    // drain one accumulator (tensor memory column offset `tcol`) to rows t0.. of `map_out`
-    auto drain = [&](uint32_t full_bar, uint32_t parity, uint32_t empty_bar, uint32_t tcol, const CUtensorMap *map_out, int t0, int b) -> bool {
-      if (epi_tid == 0) {
-        int good = mbar_wait(full_bar, parity, abort_flag) ? 1 : 0;
-        bulk_wait_read<0>();  // the previous store has drained the staging buffer
-        *epi_ok = good;
-      }
+    auto drain = [&](uint32_t full_bar, uint32_t parity, uint32_t empty_bar, uint32_t tcol, uint16_t *out, int64_t sr, int t0) -> bool {
+      if (epi_tid == 0) *epi_ok = mbar_wait(full_bar, parity, abort_flag) ? 1 : 0;
       named_bar_sync(SWP_EPI_BAR, 128);
-      if (*epi_ok == 0) return false;
+      const bool good = *epi_ok != 0;
+      named_bar_sync(SWP_EPI_BAR, 128);   // everyone has read the verdict before the next drain overwrites it
+      if (!good) return false;
       tc_fence_after_sync();
       const uint32_t taddr = tcol + ((uint32_t)(quarter * 32) << 16);
+      uint16_t *dst = out + (int64_t)(t0 + rr) * sr;
+      const bool in_range = t0 + rr < p.M;
 #pragma unroll
       for (int g = 0; g < NH / 32; g++) {
         uint32_t v[32];
         tmem_ld_x32(taddr + g * 32, v);
         tmem_ld_wait();
+        if (in_range) {
 #pragma unroll
-        for (int q4 = 0; q4 < 4; q4++) {
-          const int col = g * 32 + q4 * 8;
-          const int bx = col / OT::BOXK;
-          const int cc = (col % OT::BOXK) / 8;
-          const int sw = OT::SW_BYTES == 128 ? (rr & 7) : OT::SW_BYTES == 64 ? ((rr >> 1) & 3) : ((rr >> 2) & 1);
-          const uint32_t a = stage + bx * OT::BOX_BYTES + rr * OT::SW_BYTES + ((cc ^ sw) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(pack2<BF16>(v[q4 * 8 + 0], v[q4 * 8 + 1])),
-                       "r"(pack2<BF16>(v[q4 * 8 + 2], v[q4 * 8 + 3])), "r"(pack2<BF16>(v[q4 * 8 + 4], v[q4 * 8 + 5])),
-                       "r"(pack2<BF16>(v[q4 * 8 + 6], v[q4 * 8 + 7]))
-                       : "memory");
+          for (int q4 = 0; q4 < 4; q4++)
+            *reinterpret_cast<uint4 *>(dst + g * 32 + q4 * 8) =
+                make_uint4(pack2<BF16>(v[q4 * 8 + 0], v[q4 * 8 + 1]), pack2<BF16>(v[q4 * 8 + 2], v[q4 * 8 + 3]),
+                           pack2<BF16>(v[q4 * 8 + 4], v[q4 * 8 + 5]), pack2<BF16>(v[q4 * 8 + 6], v[q4 * 8 + 7]));
         }
       }
       tc_fence_before_sync();
       mbar_arrive(empty_bar);
-      fence_proxy_async_smem();
-      named_bar_sync(SWP_EPI_BAR, 128);
-      if (epi_tid == 0) {
-#pragma unroll
-        for (int bx = 0; bx < OT::NBOX; bx++) tma_store_3d(map_out, stage + bx * OT::BOX_BYTES, bx * OT::BOXK, t0, b);
-        bulk_commit();
-      }
       return true;
     };
     sweep_walk(
@@ -374,16 +361,15 @@ band_bwd_sweep_kernel(const __grid_constant__ CUtensorMap map_band, const __grid
           const int slot = pt % nslots;
           const uint32_t parity = (col_bits >> slot) & 1u;
           col_bits ^= 1u << slot;
-          return drain(bar_tfull(slot), parity, bar_tempty(slot), tmem_col(slot), &map_gk, pt * 128, b);
+          return drain(bar_tfull(slot), parity, bar_tempty(slot), tmem_col(slot), p.gk + b * p.gk_sb, p.gk_sr, pt * 128);
         },
         [&](int b, int r) {
           const int as = nrow & 1;
           const uint32_t parity = (nrow >> 1) & 1;
           ++nrow;
-          return drain(bar_nfull(as), parity, bar_nempty(as), tmem_row(as), &map_gq, r * TILE, b);
+          return drain(bar_nfull(as), parity, bar_nempty(as), tmem_row(as), p.gq + b * p.gq_sb, p.gq_sr, r * TILE);
         },
         [&](bool) { return true; });
-    if (epi_tid == 0) bulk_wait_all();
   }
 
   // ---------------- teardown ----------------
