@@ -81,7 +81,11 @@ enum {
   /* wmm_band_softmax / wmm_band_softmax_bwd only: out-of-sequence slots take part in the softmax with the score
    * stored there (window_matmul writes 0), which is what a plain torch softmax over the band does
    * (tests/test_attention.py:60-61).  Without this flag those slots get probability exactly 0. */
-  WMM_FLAG_SOFTMAX_KEEP_PADDING = 1u << 3
+  WMM_FLAG_SOFTMAX_KEEP_PADDING = 1u << 3,
+  /* wmm_window_bwd only: take the one-sweep kernel (each box of grad_A staged once for both products) whenever the
+   * shape allows it, also for small problems where the library would choose the two-pass kernel because the boxes a
+   * CTA replays at the start of its run outweigh the saving (testing the kernel on small cases). */
+  WMM_FLAG_PREFER_SWEEP = 1u << 4
 };
 
 /* A (batch, rows, cols) operand addressed by ELEMENT strides: either of the two inner strides may be

@@ -317,7 +317,10 @@ bool sweep_eligible(const Problem &pn, const Problem &pt) {
   const int D = pn.w / 128;
   if (2 * D + 2 > SweepSmem<32>::MAX_SLOTS || (2 * D + 4) * pn.N > 512) return false;
   if (pn.lo != 0 || pn.hi != pn.M || y_position_major(pn)) return false;
-  return true;
+  // A run that starts inside a sequence replays D (2D + 1) boxes; with short runs (few row tiles per CTA) that costs
+  // more than the second pass of the two-pass kernel.
+  const int64_t row_tiles = (int64_t)pn.B * ((pn.M + TILE - 1) / TILE);
+  return (pn.flags & WMM_FLAG_PREFER_SWEEP) != 0 || row_tiles >= 8ll * sm_count();
 }
 
 template <bool BF16, int NH> cudaError_t launch_sweep(const Problem &pn, const Problem &pt, cudaStream_t stream) {

@@ -194,13 +194,22 @@ def test_window_backward_one_sweep(wm, shape, dtype):
     q, kt, gb = H.to_dev(d["q"], dtype), H.to_dev(d["kt"], dtype), H.to_dev(g_band, dtype)
     gq = torch.full((B, M, Nn), float("nan"), dtype=dtype, device="cuda")
     gkt = torch.full((B, M, Nn), float("nan"), dtype=dtype, device="cuda")
-    before = N.launch_count()
-    wm.window_matmul_backward(q, kt.transpose(-1, -2), w, gb, out=(gq, gkt))
-    assert N.launch_count() - before == 1
+    old = wm.set_flags(N.FLAG_REQUIRE_TENSOR | N.FLAG_PREFER_SWEEP)
+    try:
+        before = N.launch_count()
+        wm.window_matmul_backward(q, kt.transpose(-1, -2), w, gb, out=(gq, gkt))
+        assert N.launch_count() - before == 1
+    finally:
+        wm.set_flags(old)
     torch.cuda.synchronize()
     assert N.device_status() == 0
     H.assert_lowp_close(gq, want_gq, "grad_q %s" % (shape,))
     H.assert_lowp_close(gkt, want_gk.transpose(0, 2, 1), "grad_k %s" % (shape,))
+    # the library's own choice for the same problem (the two-pass kernel below 8 row tiles per SM) agrees
+    gq2, gk2 = wm.window_matmul_backward(q, kt.transpose(-1, -2), w, gb)
+    torch.cuda.synchronize()
+    H.assert_lowp_close(gq2, want_gq, "grad_q, default choice %s" % (shape,))
+    H.assert_lowp_close(gk2.transpose(-1, -2), want_gk.transpose(0, 2, 1), "grad_k, default choice %s" % (shape,))
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
