@@ -33,7 +33,7 @@ struct NtParams {
 template <int NH> struct NtSmem {
   using OT = KMajorTile<NH>;
   static constexpr int QS = 2;
-  static constexpr int KS = NH >= 128 ? 2 : 4;
+  static constexpr int KS = NH >= 128 ? 3 : 4;
   static constexpr int STAGE_HALF = TILE * 128;  // 128 lines x 64 columns x 2 bytes
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + QS * OT::BYTES;
