@@ -628,15 +628,18 @@ def run_seq_sharded(args, torch, impl, N_, rank, world, dev):
     # partial grad_V and grad_K rows together after the backward ones.  They run in stream order: overlapping
     # them on a second stream measured slower, because the contraction kernels are persistent (one CTA per
     # SM for the whole launch) and a concurrent NCCL kernel waits for an SM until they finish.
-    def step():
-        kt_ext, v_ext = halo([kt, v])
+    # The six contractions between the exchanges are captured once as a CUDA graph: at 8 GPUs they take ~0.4 ms per
+    # rank, less than the host needs to issue them one by one.  The NCCL exchanges stay outside the graph (capturing
+    # torch's batched send/recv hung in this build's trial; "launch" in the JSON line says which form ran).
+    parts = {}
+
+    def contractions(kt_ext, v_ext):
         impl.band_nt(q, kt_ext, w, other_off=off, seq=seq, out=a)
         impl.band_n(a, v_ext, w, other_off=off, seq=seq, out=o)
         impl.band_nt(go, v_ext, w, other_off=off, seq=seq, out=ga)
-        gv_part = impl.band_t(a, go, w, other_rows=ext, other_off=off, seq=seq)
+        parts["gv"] = impl.band_t(a, go, w, other_rows=ext, other_off=off, seq=seq)
         impl.band_n(ga, kt_ext, w, other_off=off, seq=seq, out=gq)
-        gk_part = impl.band_t(ga, q, w, other_rows=ext, other_off=off, seq=seq)
-        return unhalo([gv_part, gk_part])
+        parts["gk"] = impl.band_t(ga, q, w, other_rows=ext, other_off=off, seq=seq)
 
     def barrier():
         torch.cuda.synchronize(dev)
@@ -644,19 +647,44 @@ def run_seq_sharded(args, torch, impl, N_, rank, world, dev):
             dist.barrier()
         torch.cuda.synchronize(dev)
 
-    for _ in range(max(3, args.warmup)):
-        step()
-    barrier()
-    launches0 = N_.launch_count()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(dev.index) as clocks:
-        ev0.record()
-        for _ in range(args.steps):
+    stream = torch.cuda.Stream(device=dev)
+    graph = None
+    with torch.cuda.stream(stream):
+        def step():
+            kt_ext, v_ext = halo([kt, v])   # views of the same storage every step: only the margins are written
+            if graph is not None:
+                graph.replay()
+            else:
+                contractions(kt_ext, v_ext)
+            return unhalo([parts["gv"], parts["gk"]])
+
+        for _ in range(max(3, args.warmup)):
             step()
-        ev1.record()
-        torch.cuda.synchronize(dev)
-    barrier()
-    launches = N_.launch_count() - launches0
+        stream.synchronize()
+        l0 = N_.launch_count()
+        step()
+        launches_per_step = N_.launch_count() - l0
+        stream.synchronize()
+        if not args.no_graph:
+            kt_ext, v_ext = halo([kt, v])
+            stream.synchronize()
+            g_ = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g_, stream=stream):
+                contractions(kt_ext, v_ext)
+            graph = g_
+            for _ in range(2):
+                step()
+            stream.synchronize()
+        barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(dev.index) as clocks:
+            ev0.record(stream)
+            for _ in range(args.steps):
+                step()
+            ev1.record(stream)
+            stream.synchronize()
+        barrier()
+    launches = launches_per_step * args.steps
     if N_.device_status() != 0:
         raise SystemExit("bench.py: a kernel abandoned a bounded wait; numbers are void")
     t = torch.tensor([ev0.elapsed_time(ev1)], dtype=torch.float64, device=dev)
@@ -672,7 +700,8 @@ def run_seq_sharded(args, torch, impl, N_, rank, world, dev):
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": us / 1e3, "higher_is_better": False,
             "scaling": "strong", "vs_baseline": None, "dtype": dt.replace("fp", "f"), "data": "synthetic",
             "config": {"workload": workload_name(args.workload), "parallelism": "sequence-sharded x%d, w-row halo exchange (NCCL send/recv)" % world,
-                       "rows_per_gpu": Ml, "halo_bytes_per_rank_step": halo_bytes, "launch": "stream launches",
+                       "rows_per_gpu": Ml, "halo_bytes_per_rank_step": halo_bytes,
+                       "launch": "cuda graph of the six contractions between two NCCL exchanges" if graph is not None else "stream launches",
                        "l2": "no flush: one step touches %.0f MB per GPU" % (total_bytes / world / 1e6)},
             "step_roofline": {"alg_MB": round(total_bytes / 1e6, 1), "alg_GFLOP": round(total_flops / 1e9, 1),
                               "achieved_GBps": round(total_bytes / (us * 1e-6) / 1e9, 1),
