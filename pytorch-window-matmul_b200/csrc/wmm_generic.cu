@@ -253,7 +253,11 @@ cudaError_t launch_typed(const Problem &p, cudaStream_t stream) {
 // rarely here; short sequences: waste) the 64 x 64 ones.
 template <typename T, bool SPLIT> cudaError_t launch_prim(Primitive prim, const Problem &p, cudaStream_t s) {
   constexpr bool F32 = sizeof(T) == 4;
-  const bool big = F32 && p.M >= 512;
+  // large tiles only when there are enough of them to fill the device twice (B200: 148 SMs); a small problem is
+  // spread over more CTAs with the 64 x 64 tiles
+  const int64_t big_rows = (int64_t)p.B * (((prim == BAND_T ? p.Mo : p.M) + 127) / 128);
+  const int64_t big_cols = prim == BAND_NT ? (128 + 2 * (int64_t)p.w + 127) / 128 : (p.N + 63) / 64;
+  const bool big = F32 && p.M >= 512 && big_rows * big_cols >= 296;
   switch (prim) {
     case BAND_NT:
       if (F32 && big && p.w >= 32) return launch_typed<T, BAND_NT, SPLIT, F32 ? 128 : 64, F32 ? 128 : 64>(p, s);
