@@ -18,7 +18,7 @@ def _declared():
 def test_header_declares_the_expected_entry_points():
     names = _declared()
     for n in ("wmm_band_nt", "wmm_band_n", "wmm_band_t", "wmm_window_bwd", "wmm_unwindow_bwd", "wmm_version",
-              "wmm_last_error_string"):
+              "wmm_last_error_string", "wmm_band_softmax", "wmm_band_softmax_bwd", "wmm_query_path", "wmm_device_status"):
         assert n in names
 
 
@@ -62,6 +62,23 @@ def test_argument_validation_needs_no_gpu():
     assert N.lib.wmm_status_string(-6) == b"WMM_ERR_CUDA"
 
 
+def test_band_softmax_argument_validation_needs_no_gpu():
+    from window_matmul import _native as N
+
+    g = N.geometry(2, 8, 0, 2)
+    assert N.lib.wmm_band_softmax(None, None, g, N.BF16, 1.0, 0, None) == -1          # NULL band pointers
+    assert N.lib.wmm_band_softmax(256, 256, None, N.BF16, 1.0, 0, None) == -1         # NULL geometry
+    assert N.lib.wmm_band_softmax(256, 264, g, N.BF16, 1.0, 0, None) == -4            # not 16-byte aligned
+    assert b"16-byte" in N.lib.wmm_last_error_string()
+    assert N.lib.wmm_band_softmax(256, 256, g, 9, 1.0, 0, None) == -3                 # unknown dtype
+    assert N.lib.wmm_band_softmax(256, 256, g, N.BF16, float("nan"), 0, None) == -2   # NaN scale
+    assert N.lib.wmm_band_softmax(256, 256, g, N.BF16, 1.0, N.FLAG_SPLIT_ROUNDING, None) == -7   # a flag of the contractions
+    assert N.lib.wmm_band_softmax_bwd(256, None, 256, g, N.BF16, 1.0, 0, None) == -1  # backward needs both inputs
+    before = N.launch_count()
+    assert N.lib.wmm_band_softmax(None, None, N.geometry(0, 8, 0, 2), N.BF16, 1.0, 0, None) == 0   # empty: no launch
+    assert N.launch_count() == before
+
+
 def test_python_surface_matches_the_reference():
     import inspect
 
@@ -91,3 +108,21 @@ def test_cpu_tensors_are_refused_loudly():
     assert wm.window_matmul(q, k, 0).shape == (2, 4, 1)
     a, v = torch.randn(2, 4, 1), torch.randn(2, 4, 3)
     assert torch.equal(wm.unwindow_matmul(a, v, 0), a * v)
+
+
+def test_public_header_is_plain_c_and_cxx(tmp_path):
+    """include/wmm_b200.h is the whole contract of the native boundary: it must compile on its own as C and as C++
+    (no torch, CUDA or project headers behind it)."""
+    import shutil
+    import subprocess
+
+    if not shutil.which("gcc") or not shutil.which("g++"):
+        pytest.skip("no host compiler")
+    src = tmp_path / "use.c"
+    src.write_text('#include "wmm_b200.h"\nint main(void) { wmm_geometry g = {1, 8, 4, 2, 8, 0, 0, 8}; wmm_operand o = {0, 32, 4, 1};\n'
+                   '  return (int)(g.window + o.stride_c) * 0 + (WMM_OK != 0) + (sizeof(wmm_geometry) != 32); }\n')
+    inc = os.path.join(ROOT, "include")
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-pedantic", "-fsyntax-only", "-I", inc, str(src)], check=True)
+    cxx = tmp_path / "use.cc"
+    cxx.write_text(src.read_text())
+    subprocess.run(["g++", "-std=c++17", "-Wall", "-Werror", "-fsyntax-only", "-I", inc, str(cxx)], check=True)
