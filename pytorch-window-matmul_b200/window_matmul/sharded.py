@@ -27,6 +27,7 @@ import torch.distributed as dist
 
 # the submodule, not the function of the same name that the package exports
 _ops = importlib.import_module(__package__ + ".window_matmul")
+_sm = importlib.import_module(__package__ + ".softmax")
 
 
 class _Primitives:
@@ -36,6 +37,8 @@ class _Primitives:
     band_nt = staticmethod(_ops.band_nt)
     band_n = staticmethod(_ops.band_n)
     band_t = staticmethod(_ops.band_t)
+    band_softmax = staticmethod(_sm.band_softmax)
+    band_softmax_backward = staticmethod(_sm.band_softmax_backward)
 
 
 primitives = _Primitives()
@@ -213,6 +216,35 @@ def seq_parallel_unwindow_matmul(inp: torch.Tensor, other: torch.Tensor, window_
     v = other.reshape(-1, seq_len, hidden)
     out = _SeqUnwindowMatmul.apply(a, v, window_size, group)
     return out.reshape(*dims, seq_len, hidden)
+
+
+class _SeqWindowSoftmax(torch.autograd.Function):
+    """Band rows never cross ranks, so the softmax of a sequence shard needs no communication: only the shard's place
+    in the global sequence, for the out-of-sequence slots of the first and last rank."""
+
+    @staticmethod
+    def forward(ctx, scores, scale, mask, group):
+        Ml, w = scores.shape[1], (scores.shape[2] - 1) // 2
+        seq = _local_seq(Ml, w, group)
+        probs = primitives.band_softmax(scores, scale, mask, other_off=w, seq=seq, other_rows=Ml + 2 * w)
+        ctx.save_for_backward(probs)
+        ctx.args = (scale, mask, w, seq, Ml)
+        return probs
+
+    @staticmethod
+    def backward(ctx, grad_probs):
+        (probs,) = ctx.saved_tensors
+        scale, mask, w, seq, Ml = ctx.args
+        gs = primitives.band_softmax_backward(probs, grad_probs.contiguous(), scale, mask, other_off=w, seq=seq,
+                                              other_rows=Ml + 2 * w)
+        return gs, None, None, None
+
+
+def seq_parallel_window_softmax(scores: torch.Tensor, scale: float = 1.0, mask: bool = True, group=None) -> torch.Tensor:
+    """`window_softmax` on a sequence shard: scores (*, Ml, 2w+1) = this rank's band rows."""
+    lead = scores.shape[:-2]
+    flat = scores.reshape(-1, scores.shape[-2], scores.shape[-1])
+    return _SeqWindowSoftmax.apply(flat, float(scale), bool(mask), group).reshape(*lead, *scores.shape[-2:])
 
 
 def shard_batch(t: torch.Tensor, group=None) -> torch.Tensor:

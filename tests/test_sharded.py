@@ -60,6 +60,22 @@ class _CheckerPrimitives:
         return o
 
 
+    @staticmethod
+    def band_softmax(scores, scale=1.0, mask=True, *, other_off=0, seq=None, other_rows=None, out=None):
+        B, M, W = scores.shape
+        w = (W - 1) // 2
+        lo, hi = (0, M if other_rows is None else other_rows) if seq is None else seq
+        p = torch.arange(M)[:, None] + torch.arange(W)[None, :] - w + other_off
+        s = scores * scale
+        if mask:
+            s = s.masked_fill(~((p >= lo) & (p < hi)), float("-inf"))
+        return torch.softmax(s, dim=-1)
+
+    @staticmethod
+    def band_softmax_backward(probs, grad_probs, scale=1.0, mask=True, *, other_off=0, seq=None, other_rows=None, out=None):
+        return scale * probs * (grad_probs - (grad_probs * probs).sum(-1, keepdim=True))
+
+
 def _worker(rank, world, port, shape, out_dir):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -82,8 +98,14 @@ def _worker(rank, world, port, shape, out_dir):
         a.retain_grad()
         o = sharded.seq_parallel_unwindow_matmul(a, vl, w)
         o.backward(go[:, sl])
+        # the attention block: scores -> masked softmax -> values, all three sharded operators
+        q2, k2, v2 = (t[:, sl].clone().requires_grad_(True) for t in (q, k, v))
+        pr = sharded.seq_parallel_window_softmax(sharded.seq_parallel_window_matmul(q2, k2.transpose(-1, -2), w), 0.5, True)
+        ob = sharded.seq_parallel_unwindow_matmul(pr, v2, w)
+        ob.backward(go[:, sl])
         np.savez(os.path.join(out_dir, "rank%d.npz" % rank), a=a.detach().numpy(), o=o.detach().numpy(), gq=ql.grad.numpy(),
-                 gk=kl.grad.numpy(), gv=vl.grad.numpy(), ga=a.grad.numpy())
+                 gk=kl.grad.numpy(), gv=vl.grad.numpy(), ga=a.grad.numpy(), ob=ob.detach().numpy(), bq=q2.grad.numpy(),
+                 bk=k2.grad.numpy(), bv=v2.grad.numpy())
         # batch sharding: contiguous blocks, no communication
         blk = sharded.shard_batch(torch.arange(7))
         per = -(-7 // world)
@@ -111,6 +133,16 @@ def test_sequence_sharded_operators_match_the_unsharded_oracle(tmp_path, world, 
     np.testing.assert_allclose(cat("gq"), gq, rtol=1e-12, atol=1e-12)
     np.testing.assert_allclose(cat("gk"), gk.transpose(0, 2, 1), rtol=1e-12, atol=1e-12)
     np.testing.assert_allclose(cat("gv"), gv, rtol=1e-12, atol=1e-12)
+    # attention block against the dense formulation on the whole sequence
+    qt, kt_, vt = (torch.from_numpy(x).requires_grad_(True) for x in (q, k, v))
+    i = torch.arange(M)
+    inside = (i[:, None] - i[None, :]).abs() <= w
+    dense = torch.softmax((qt @ kt_.transpose(-1, -2) * 0.5).masked_fill(~inside, float("-inf")), -1) @ vt
+    dense.backward(torch.from_numpy(go))
+    np.testing.assert_allclose(cat("ob"), dense.detach().numpy(), rtol=1e-10, atol=1e-12)
+    np.testing.assert_allclose(cat("bq"), qt.grad.numpy(), rtol=1e-10, atol=1e-12)
+    np.testing.assert_allclose(cat("bk"), kt_.grad.numpy(), rtol=1e-10, atol=1e-12)
+    np.testing.assert_allclose(cat("bv"), vt.grad.numpy(), rtol=1e-10, atol=1e-12)
 
 
 def test_shard_shorter_than_the_window_is_refused():

@@ -44,11 +44,17 @@ def _worker(rank, world, port, shape, dtype_name, out_dir):
         a.retain_grad()
         o = sharded.seq_parallel_unwindow_matmul(a, vl, w)
         o.backward(go[:, sl].to(dtype).to(dev))
+        # the attention block with the band softmax between the sharded operators
+        q2, k2, v2 = (t[:, sl].to(dtype).to(dev).requires_grad_(True) for t in (q, k, v))
+        pr = sharded.seq_parallel_window_softmax(sharded.seq_parallel_window_matmul(q2, k2.transpose(-1, -2), w), 0.5, True)
+        ob = sharded.seq_parallel_unwindow_matmul(pr, v2, w)
+        ob.backward(go[:, sl].to(dtype).to(dev))
         torch.cuda.synchronize()
         assert _native.device_status() == 0
         np.savez(os.path.join(out_dir, "rank%d.npz" % rank), **{
             key: t.detach().float().cpu().numpy()
-            for key, t in dict(a=a, o=o, gq=ql.grad, gk=kl.grad, gv=vl.grad, ga=a.grad).items()})
+            for key, t in dict(a=a, o=o, gq=ql.grad, gk=kl.grad, gv=vl.grad, ga=a.grad, ob=ob, bq=q2.grad, bk=k2.grad,
+                               bv=v2.grad).items()})
         dist.barrier()
     finally:
         dist.destroy_process_group()
@@ -76,3 +82,12 @@ def test_sequence_sharded_on_gpus(tmp_path, dtype_name, shape):
     rel = 2e-5 if dtype == torch.float32 else 4e-2  # bf16: the band itself is rounded before it is reused
     for key, want in dict(a=a, o=o, ga=ga, gq=gq, gk=gk.transpose(0, 2, 1), gv=gv).items():
         H.assert_lowp_close(cat(key), want, key, rel=rel if key != "a" else min(rel, 1e-2))
+    # attention block (scores * 0.5, masked softmax, values) against the dense float64 formulation
+    qt, kt_, vt = (torch.from_numpy(x).double().requires_grad_(True) for x in (q, k, v))
+    i = torch.arange(M)
+    inside = (i[:, None] - i[None, :]).abs() <= w
+    dense = torch.softmax((qt @ kt_.transpose(-1, -2) * 0.5).masked_fill(~inside, float("-inf")), -1) @ vt
+    dense.backward(torch.from_numpy(go).double())
+    rel_b = 1e-4 if dtype == torch.float32 else 6e-2
+    for key, want in dict(ob=dense.detach(), bq=qt.grad, bk=kt_.grad, bv=vt.grad).items():
+        H.assert_lowp_close(cat(key), want.numpy(), key, rel=rel_b)
