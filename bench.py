@@ -624,22 +624,30 @@ def run_seq_sharded(args, torch, impl, N_, rank, world, dev):
     halo = (lambda xs: sharded.exchange_halo_many(xs, w)) if world > 1 else (lambda xs: xs)
     unhalo = (lambda xs: sharded.reduce_halo_many(xs, w)) if world > 1 else (lambda xs: xs)
 
-    # Two neighbour exchanges per step: the K^T and V halos together before the forward contractions, the
-    # partial grad_V and grad_K rows together after the backward ones.  They run in stream order: overlapping
-    # them on a second stream measured slower, because the contraction kernels are persistent (one CTA per
-    # SM for the whole launch) and a concurrent NCCL kernel waits for an SM until they finish.
-    # The six contractions between the exchanges are captured once as a CUDA graph: at 8 GPUs they take ~0.4 ms per
-    # rank, less than the host needs to issue them one by one.  The NCCL exchanges stay outside the graph (capturing
-    # torch's batched send/recv hung in this build's trial; "launch" in the JSON line says which form ran).
+    # Two neighbour exchanges per step: the K^T and V halos together before the forward contractions, the partial
+    # grad_K and grad_V rows together after the backward ones.
+    #   --exchange peer (default): each exchange is ONE kernel of the library reading the neighbours' rows through peer
+    #     memory (window_matmul/peer_halo.py); the whole step, exchanges included, replays as one CUDA graph.
+    #   --exchange nccl: torch.distributed send/recv pairs (window_matmul/sharded.py) around a graph of the six
+    #     contractions; each exchange costs ~120 us of host time per rank, which binds the step at 8 ranks.
+    # Overlapping the exchanges with the contractions on a second stream measured slower (persistent kernels: a concurrent
+    # kernel waits for an SM until they finish), so they run in stream order.
+    peer = world > 1 and args.exchange == "peer"
     parts = {}
+    if peer:
+        from window_matmul.peer_halo import PeerHalo
+
+        ph = PeerHalo(2, B, Ml, N, w, dtype, dev)
+        ph.local(0).copy_(kt)
+        ph.local(1).copy_(v)
 
     def contractions(kt_ext, v_ext):
         impl.band_nt(q, kt_ext, w, other_off=off, seq=seq, out=a)
         impl.band_n(a, v_ext, w, other_off=off, seq=seq, out=o)
         impl.band_nt(go, v_ext, w, other_off=off, seq=seq, out=ga)
-        parts["gv"] = impl.band_t(a, go, w, other_rows=ext, other_off=off, seq=seq)
+        parts["gv"] = impl.band_t(a, go, w, other_rows=ext, other_off=off, seq=seq, out=ph.partial(1) if peer else None)
         impl.band_n(ga, kt_ext, w, other_off=off, seq=seq, out=gq)
-        parts["gk"] = impl.band_t(ga, q, w, other_rows=ext, other_off=off, seq=seq)
+        parts["gk"] = impl.band_t(ga, q, w, other_rows=ext, other_off=off, seq=seq, out=ph.partial(0) if peer else None)
 
     def barrier():
         torch.cuda.synchronize(dev)
@@ -650,13 +658,23 @@ def run_seq_sharded(args, torch, impl, N_, rank, world, dev):
     stream = torch.cuda.Stream(device=dev)
     graph = None
     with torch.cuda.stream(stream):
-        def step():
+        def raw_step():
+            if peer:
+                kt_ext, v_ext = ph.exchange()
+                contractions(kt_ext, v_ext)
+                return ph.reduce()
             kt_ext, v_ext = halo([kt, v])   # views of the same storage every step: only the margins are written
             if graph is not None:
                 graph.replay()
             else:
                 contractions(kt_ext, v_ext)
             return unhalo([parts["gv"], parts["gk"]])
+
+        def step():
+            if peer and graph is not None:
+                graph.replay()
+            else:
+                raw_step()
 
         for _ in range(max(3, args.warmup)):
             step()
@@ -666,11 +684,16 @@ def run_seq_sharded(args, torch, impl, N_, rank, world, dev):
         launches_per_step = N_.launch_count() - l0
         stream.synchronize()
         if not args.no_graph:
-            kt_ext, v_ext = halo([kt, v])
-            stream.synchronize()
             g_ = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g_, stream=stream):
-                contractions(kt_ext, v_ext)
+            if peer:
+                barrier()
+                with torch.cuda.graph(g_, stream=stream):
+                    raw_step()
+            else:
+                kt_ext, v_ext = halo([kt, v])
+                stream.synchronize()
+                with torch.cuda.graph(g_, stream=stream):
+                    contractions(kt_ext, v_ext)
             graph = g_
             for _ in range(2):
                 step()
@@ -699,9 +722,11 @@ def run_seq_sharded(args, torch, impl, N_, rank, world, dev):
             "metric": "fwd+bwd window+unwindow us (%s, sequence-sharded)" % args.workload, "value": us, "unit": "us", "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": us / 1e3, "higher_is_better": False,
             "scaling": "strong", "vs_baseline": None, "dtype": dt.replace("fp", "f"), "data": "synthetic",
-            "config": {"workload": workload_name(args.workload), "parallelism": "sequence-sharded x%d, w-row halo exchange (NCCL send/recv)" % world,
+            "config": {"workload": workload_name(args.workload), "parallelism": "sequence-sharded x%d, w-row halo exchange" % world,
                        "rows_per_gpu": Ml, "halo_bytes_per_rank_step": halo_bytes,
-                       "launch": "cuda graph of the six contractions between two NCCL exchanges" if graph is not None else "stream launches",
+                       "exchange": ("peer memory: one kernel of the library per exchange" if peer else "NCCL send/recv (torch.distributed)"),
+                       "launch": ("stream launches" if graph is None else "one cuda graph per step (exchanges and contractions)" if peer
+                                  else "cuda graph of the six contractions between two NCCL exchanges"),
                        "l2": "no flush: one step touches %.0f MB per GPU" % (total_bytes / world / 1e6)},
             "step_roofline": {"alg_MB": round(total_bytes / 1e6, 1), "alg_GFLOP": round(total_flops / 1e9, 1),
                               "achieved_GBps": round(total_bytes / (us * 1e-6) / 1e9, 1),
@@ -730,6 +755,8 @@ def main():
                     help="multi-GPU partitioning: batch entries (default) or sequence rows with halo exchange (default for c4)")
     ap.add_argument("--e2e-chunks", type=int, default=8, help="batch chunks of the host-buffer leg")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="sequence-sharded mode: halo exchange through peer memory (one library kernel) or NCCL send/recv")
     ap.add_argument("--block", default="auto", choices=["auto", "on", "off"],
                     help="also time the attention block with the band softmax between the operators (auto: config 5)")
     args = ap.parse_args()

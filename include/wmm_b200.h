@@ -181,6 +181,41 @@ WMM_API int wmm_band_softmax(const void *scores, void *probs, const wmm_geometry
 WMM_API int wmm_band_softmax_bwd(const void *probs, const void *grad_probs, void *grad_scores,
                                  const wmm_geometry *g, int dtype, float scale, unsigned flags, void *stream);
 
+/* ---- sequence shards: neighbour exchange through peer memory ---------------------------------- */
+
+/* A sharded operand in its "extended" buffer: contiguous (batch, rows + 2*window, cols) = w margin rows, the rank's own
+ * rows, w margin rows.  `local` is this rank's buffer, `lower` / `upper` the SAME tensor's buffer on the rank that owns
+ * the rows before / after (pointers that this device can load from: peer-mapped or symmetric memory), NULL at an end of
+ * the global sequence.  All 16-byte aligned. */
+typedef struct wmm_halo_buffer {
+  void *local;
+  const void *lower;
+  const void *upper;
+} wmm_halo_buffer;
+
+/* Flag words of the hand-shake.  `mine`, `lower`, `upper`: this rank's and the neighbours' blocks of at least 4
+ * 32-bit words in memory every neighbour can read AND write (word 0: ready epoch, word 1 / 2: acknowledgement written
+ * by the lower / upper neighbour), zero before the first call; NULL for a missing neighbour.  `counters`: 2 words of
+ * plain device memory of this rank, zero before the first call. */
+typedef struct wmm_halo_flags {
+  unsigned *mine;
+  unsigned *lower;
+  unsigned *upper;
+  unsigned *counters;
+} wmm_halo_flags;
+
+/* One neighbour exchange for up to 4 tensors of the same shape, in ONE kernel launch on `stream`:
+ *   accumulate == 0: each buffer's lower margin <- the lower neighbour's last `window` own rows, upper margin <- the upper
+ *                    neighbour's first `window` own rows (halo rows of K^T and V before the forward contractions);
+ *   accumulate != 0: this rank's first `window` own rows += the lower neighbour's upper margin, its last `window` own rows
+ *                    += the upper neighbour's lower margin (partial grad_K / grad_V rows after the backward contractions;
+ *                    needs rows >= 2*window).
+ * Every rank of the sequence group must issue the same sequence of these calls.  The kernel waits (at most ~1 s per
+ * wait) for the neighbours' kernels of the same call; a wait that runs out sets bit 5 of wmm_device_status().  The
+ * reference has no multi-GPU code; this replaces the send/recv pairs of a host communication library on that path. */
+WMM_API int wmm_halo_pull(const wmm_halo_buffer *buffers, int count, const wmm_halo_flags *flags, int batch, int rows,
+                          int cols, int window, int dtype, int accumulate, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

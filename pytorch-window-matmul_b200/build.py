@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "window_matmul", "libwmm_b200.so")
-SOURCES = ["wmm_api.cu", "wmm_generic.cu", "wmm_tc.cu", "wmm_small.cu", "wmm_softmax.cu"]
+SOURCES = ["wmm_api.cu", "wmm_generic.cu", "wmm_tc.cu", "wmm_small.cu", "wmm_softmax.cu", "wmm_halo.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

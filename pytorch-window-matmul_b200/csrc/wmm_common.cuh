@@ -48,6 +48,10 @@ cudaError_t launch_small(Primitive prim, const Problem &p, cudaStream_t stream, 
 cudaError_t launch_band_softmax(bool backward, const void *in, const void *in2, void *out, const wmm_geometry &g,
                                 int dtype, float scale, bool mask, cudaStream_t stream, int *launches);
 
+// Neighbour exchange of halo rows through peer memory (wmm_halo.cu).
+cudaError_t launch_halo_pull(const wmm_halo_buffer *bufs, int count, const wmm_halo_flags &flags, int batch, int rows,
+                             int cols, int window, int dtype, bool accumulate, cudaStream_t stream, int *launches);
+
 // Launchers describe a failure (which step, which driver code) here; the API layer appends it to the
 // error string of the calling thread.
 void set_launch_detail(const char *fmt, ...);

@@ -45,6 +45,16 @@ class Geometry(ctypes.Structure):
     ]
 
 
+class HaloBuffer(ctypes.Structure):
+    """wmm_halo_buffer of include/wmm_b200.h."""
+    _fields_ = [("local", ctypes.c_void_p), ("lower", ctypes.c_void_p), ("upper", ctypes.c_void_p)]
+
+
+class HaloFlags(ctypes.Structure):
+    """wmm_halo_flags of include/wmm_b200.h."""
+    _fields_ = [("mine", ctypes.c_void_p), ("lower", ctypes.c_void_p), ("upper", ctypes.c_void_p), ("counters", ctypes.c_void_p)]
+
+
 def _load():
     if not os.path.exists(LIB_PATH):
         raise RuntimeError(
@@ -76,6 +86,8 @@ def _load():
     lib.wmm_window_bwd.argtypes = [P(Operand), P(Operand), vp, P(Operand), P(Operand), P(Geometry), i32, u32, vp]
     lib.wmm_unwindow_bwd.restype = i32
     lib.wmm_unwindow_bwd.argtypes = [vp, P(Operand), P(Operand), vp, P(Operand), P(Geometry), i32, u32, vp]
+    lib.wmm_halo_pull.restype = i32
+    lib.wmm_halo_pull.argtypes = [P(HaloBuffer), i32, P(HaloFlags), i32, i32, i32, i32, i32, i32, vp]
     lib.wmm_band_softmax.restype = i32
     lib.wmm_band_softmax.argtypes = [vp, vp, P(Geometry), i32, ctypes.c_float, u32, vp]
     lib.wmm_band_softmax_bwd.restype = i32

@@ -91,3 +91,78 @@ def test_sequence_sharded_on_gpus(tmp_path, dtype_name, shape):
     rel_b = 1e-4 if dtype == torch.float32 else 6e-2
     for key, want in dict(ob=dense.detach(), bq=qt.grad, bk=kt_.grad, bv=vt.grad).items():
         H.assert_lowp_close(cat(key), want.numpy(), key, rel=rel_b)
+
+
+def _peer_worker(rank, world, port, shape, dtype_name, out_dir):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    sys.path[:0] = [ROOT, os.path.join(ROOT, "pytorch-window-matmul_b200")]
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from window_matmul import _native
+        from window_matmul.peer_halo import PeerHalo
+
+        dtype = getattr(torch, dtype_name)
+        B, M, N, w = shape
+        Ml = M // world
+        g = torch.Generator().manual_seed(11)
+        xs = [torch.randn(B, M, N, generator=g).to(dtype) for _ in range(2)]                  # the global operands
+        ps = [[torch.randn(B, Ml + 2 * w, N, generator=g).to(dtype) for _ in range(2)] for _ in range(world)]  # partials of every rank
+        halo = PeerHalo(2, B, Ml, N, w, dtype, dev)
+        for i in range(2):
+            halo.local(i).copy_(xs[i][:, rank * Ml:(rank + 1) * Ml])
+        # three exchanges; the owners rescale their rows in between, so stale reads would show
+        for it in range(3):
+            exts = halo.exchange()
+            torch.cuda.synchronize()
+            for i in range(2):
+                padded = torch.nn.functional.pad(xs[i].float() * (2.0 ** it), (0, 0, w, w))
+                want = padded[:, rank * Ml:rank * Ml + Ml + 2 * w].to(dtype)
+                assert torch.equal(exts[i].cpu(), want), "exchange %d, tensor %d on rank %d" % (it, i, rank)
+            for i in range(2):
+                halo.local(i).mul_(2.0)
+        # reverse halo: own rows += what the neighbours computed for them
+        for i in range(2):
+            halo.partial(i).copy_(ps[rank][i])
+        own = halo.reduce()
+        torch.cuda.synchronize()
+        for i in range(2):
+            want = ps[rank][i][:, w:w + Ml].float().clone()
+            if rank > 0:
+                want[:, :w] = (want[:, :w].to(dtype).float() + ps[rank - 1][i][:, w + Ml:].float())
+            want = want.to(dtype).float()
+            if rank < world - 1:
+                want[:, Ml - w:] = (want[:, Ml - w:] + ps[rank + 1][i][:, :w].float())
+            assert torch.equal(own[i].cpu(), want.to(dtype)), "reduce, tensor %d on rank %d" % (i, rank)
+        # the same exchange replayed from a CUDA graph (the hand-shake counts epochs on the device)
+        s = torch.cuda.Stream(device=dev)
+        with torch.cuda.stream(s):
+            halo.exchange()
+            s.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=s):
+                halo.exchange()
+            for _ in range(4):
+                graph.replay()
+            s.synchronize()
+        for i in range(2):
+            padded = torch.nn.functional.pad(xs[i].float() * 8.0, (0, 0, w, w))
+            assert torch.equal(halo.ext(i).cpu(), padded[:, rank * Ml:rank * Ml + Ml + 2 * w].to(dtype))
+        assert _native.device_status() == 0
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("dtype_name,shape", [("bfloat16", (3, 512, 64, 64)), ("float32", (2, 384, 16, 24))])
+def test_peer_memory_halo_exchange(tmp_path, dtype_name, shape):
+    """wmm_halo_pull: margins from the neighbours' edge rows, reverse accumulation, repeated epochs, graph replay."""
+    import torch.multiprocessing as mp
+
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least 2 GPUs")
+    mp.spawn(_peer_worker, args=(world, _free_port(), shape, dtype_name, str(tmp_path)), nprocs=world, join=True)
