@@ -126,3 +126,28 @@ def test_public_header_is_plain_c_and_cxx(tmp_path):
     cxx = tmp_path / "use.cc"
     cxx.write_text(src.read_text())
     subprocess.run(["g++", "-std=c++17", "-Wall", "-Werror", "-fsyntax-only", "-I", inc, str(cxx)], check=True)
+
+
+def test_halo_pull_argument_validation_needs_no_gpu():
+    import ctypes as C
+
+    from window_matmul import _native as N
+
+    def call(bufs, flags, batch=2, rows=64, cols=8, window=16, dtype=N.BF16, acc=0):
+        arr = (N.HaloBuffer * len(bufs))(*bufs)
+        return N.lib.wmm_halo_pull(arr, len(bufs), C.byref(flags) if flags is not None else None, batch, rows, cols, window, dtype, acc, None)
+
+    both = N.HaloFlags(1024, 2048, 4096, 8192)
+    buf = N.HaloBuffer(256, 512, 768)
+    assert call([buf], None) == -1                                         # no flags
+    assert call([buf] * 5, both) == -2                                     # more than 4 buffers
+    assert call([buf], both, dtype=11) == -3                               # unknown dtype
+    assert call([buf], both, rows=8, window=16) == -2                      # shard shorter than the window
+    assert call([buf], both, rows=24, window=16, acc=1) == -2              # reduction needs rows >= 2 w
+    assert call([buf], both, cols=3) == -4                                 # rows that are not a multiple of 16 bytes
+    assert call([N.HaloBuffer(260, 512, 768)], both) == -4                 # unaligned buffer
+    assert call([N.HaloBuffer(256, None, 768)], both) == -1                # buffer and flags disagree on the neighbours
+    assert call([N.HaloBuffer(None, 512, 768)], both) == -1                # no local buffer
+    before = N.launch_count()
+    assert call([buf], both, batch=0) == 0                                 # empty: no launch
+    assert N.launch_count() == before
