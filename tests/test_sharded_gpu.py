@@ -166,3 +166,33 @@ def test_peer_memory_halo_exchange(tmp_path, dtype_name, shape):
     if world < 2:
         pytest.skip("needs at least 2 GPUs")
     mp.spawn(_peer_worker, args=(world, _free_port(), shape, dtype_name, str(tmp_path)), nprocs=world, join=True)
+
+
+def test_halo_pull_wait_runs_out_without_hanging():
+    """Failure detection of the exchange kernel on ONE GPU: the flag block of a 'neighbour' that never runs is plain local
+    memory that nothing sets.  The kernel's bounded waits (about a second each) run out, it returns, the status word has
+    bit 5 set, the margins are untouched and the context stays usable."""
+    import ctypes as C
+
+    sys.path[:0] = [ROOT, os.path.join(ROOT, "pytorch-window-matmul_b200")]
+    from window_matmul import _native as N
+
+    dev = torch.device("cuda", 0)
+    B, Ml, Nn, w = 2, 64, 8, 16
+    mine = torch.full((B, Ml + 2 * w, Nn), 1.0, dtype=torch.bfloat16, device=dev)
+    absent = torch.full((B, Ml + 2 * w, Nn), 7.0, dtype=torch.bfloat16, device=dev)   # stands in for the lower neighbour's buffer
+    my_flags = torch.zeros(4, dtype=torch.int32, device=dev)
+    absent_flags = torch.zeros(4, dtype=torch.int32, device=dev)                       # its ready word stays 0
+    counters = torch.zeros(2, dtype=torch.int32, device=dev)
+    torch.cuda.synchronize()
+    assert N.device_status() == 0
+    bufs = (N.HaloBuffer * 1)(N.HaloBuffer(mine.data_ptr(), absent.data_ptr(), None))
+    flags = N.HaloFlags(my_flags.data_ptr(), absent_flags.data_ptr(), None, counters.data_ptr())
+    stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    N.check(N.lib.wmm_halo_pull(bufs, 1, C.byref(flags), B, Ml, Nn, w, N.BF16, 0, stream))
+    torch.cuda.synchronize()
+    assert N.device_status() & 32, "the kernel must report the wait that ran out"
+    assert N.device_status() == 0                       # reading cleared it
+    assert (mine == 1.0).all()                          # nothing was copied from a neighbour that was not ready
+    assert int(my_flags[0]) == 1 and int(counters[0]) == 1 and int(counters[1]) == 0   # epoch advanced, CTA counter reset
+    assert float((mine.float() + 1).sum()) > 0          # the context still works
