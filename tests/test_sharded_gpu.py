@@ -196,3 +196,76 @@ def test_halo_pull_wait_runs_out_without_hanging():
     assert (mine == 1.0).all()                          # nothing was copied from a neighbour that was not ready
     assert int(my_flags[0]) == 1 and int(counters[0]) == 1 and int(counters[1]) == 0   # epoch advanced, CTA counter reset
     assert float((mine.float() + 1).sum()) > 0          # the context still works
+
+
+def _peer_chain_worker(rank, world, port, shape, dtype_name, out_dir):
+    import importlib
+
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    sys.path[:0] = [ROOT, os.path.join(ROOT, "pytorch-window-matmul_b200")]
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from window_matmul import _native
+        from window_matmul.peer_halo import PeerHalo
+
+        impl = importlib.import_module("window_matmul.window_matmul")
+        dtype = getattr(torch, dtype_name)
+        B, M, N, w = shape
+        g = torch.Generator().manual_seed(5)
+        q, k, v = (torch.randn(B, M, N, generator=g) / N ** 0.5 for _ in range(3))
+        go = torch.randn(B, M, N, generator=g)
+        Ml = M // world
+        sl = slice(rank * Ml, (rank + 1) * Ml)
+        ql, gol = q[:, sl].to(dtype).to(dev), go[:, sl].to(dtype).to(dev)
+        halo = PeerHalo(2, B, Ml, N, w, dtype, dev)      # operand 0: K^T rows, operand 1: V rows
+        halo.local(0).copy_(k[:, sl].to(dtype))
+        halo.local(1).copy_(v[:, sl].to(dtype))
+        ext, seq = Ml + 2 * w, halo.seq
+
+        def step():
+            kt_ext, v_ext = halo.exchange()
+            a = impl.band_nt(ql, kt_ext, w, other_off=w, seq=seq)
+            o = impl.band_n(a, v_ext, w, other_off=w, seq=seq)
+            ga = impl.band_nt(gol, v_ext, w, other_off=w, seq=seq)
+            impl.band_t(a, gol, w, other_rows=ext, other_off=w, seq=seq, out=halo.partial(1))
+            gq = impl.band_n(ga, kt_ext, w, other_off=w, seq=seq)
+            impl.band_t(ga, ql, w, other_rows=ext, other_off=w, seq=seq, out=halo.partial(0))
+            gk, gv = halo.reduce()
+            return dict(a=a, o=o, ga=ga, gq=gq, gk=gk, gv=gv)
+
+        step()                 # twice: the second step must not see leftovers of the first in the partial buffers
+        out = step()
+        torch.cuda.synchronize()
+        assert _native.device_status() == 0
+        np.savez(os.path.join(out_dir, "rank%d.npz" % rank), **{key: t.detach().float().cpu().numpy() for key, t in out.items()})
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("dtype_name,shape", [("bfloat16", (2, 1024, 64, 64)), ("bfloat16", (1, 4096, 128, 512))])
+def test_sequence_sharded_chain_through_peer_memory(tmp_path, dtype_name, shape):
+    """The six contractions on sequence shards with both halo exchanges done by wmm_halo_pull, against the oracle on the
+    whole sequence."""
+    import torch.multiprocessing as mp
+
+    import helpers as H
+
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least 2 GPUs")
+    mp.spawn(_peer_chain_worker, args=(world, _free_port(), shape, dtype_name, str(tmp_path)), nprocs=world, join=True)
+    B, M, N, w = shape
+    dtype = getattr(torch, dtype_name)
+    g = torch.Generator().manual_seed(5)
+    q, k, v = (H.round_to((torch.randn(B, M, N, generator=g) / N ** 0.5).numpy(), dtype) for _ in range(3))
+    go = H.round_to(torch.randn(B, M, N, generator=g).numpy(), dtype)
+    a, o, gq, gk, ga, gv = H.oracle.chain_fwd_bwd(q, np.ascontiguousarray(k.transpose(0, 2, 1)), v, w, go)
+    parts = [np.load(os.path.join(str(tmp_path), "rank%d.npz" % r)) for r in range(world)]
+    cat = lambda key: torch.from_numpy(np.concatenate([p[key] for p in parts], axis=1))  # noqa: E731
+    for key, want in dict(a=a, o=o, ga=ga, gq=gq, gk=gk.transpose(0, 2, 1), gv=gv).items():
+        H.assert_lowp_close(cat(key), want, key, rel=1e-2 if key == "a" else 4e-2)
