@@ -103,12 +103,12 @@ def band_t(band, x, window, *, other_rows=None, other_off=0, seq=None, out=None,
 # ---- the four native calls of the reference's pybind module ---------------------------------------
 
 
-def window_matmul_forward(src: torch.Tensor, other: torch.Tensor, window_size: int) -> torch.Tensor:
+def window_matmul_forward(src: torch.Tensor, other: torch.Tensor, window_size: int, out=None) -> torch.Tensor:
     """csrc/window_matmul/window_matmul.cpp:74-78 -> window_matmul_fw_cuda (window_matmul_cuda.cu:224-270).
     src (B,M,N), other (B,N,M) -> (B,M,2w+1)."""
     _mismatch(src.dim() == 3 and other.dim() == 3)
     _mismatch(src.size(0) == other.size(0) and src.size(1) == other.size(2) and src.size(2) == other.size(1))
-    return band_nt(src, other.transpose(-1, -2), window_size)
+    return band_nt(src, other.transpose(-1, -2), window_size, out=out)
 
 
 def window_matmul_backward(src, other, window_size, grad_output, need=(True, True), out=None):
@@ -137,13 +137,13 @@ def window_matmul_backward(src, other, window_size, grad_output, need=(True, Tru
     return gq, gk
 
 
-def unwindow_matmul_forward(src: torch.Tensor, other: torch.Tensor, window_size: int) -> torch.Tensor:
+def unwindow_matmul_forward(src: torch.Tensor, other: torch.Tensor, window_size: int, out=None) -> torch.Tensor:
     """window_matmul.cpp:87-91 -> unwindow_matmul_fw_cuda (window_matmul_cuda.cu:321-358).
     src (B,M,2w+1), other (B,M,N) -> (B,M,N)."""
     _mismatch(src.dim() == 3 and other.dim() == 3)
     _mismatch(src.size(0) == other.size(0) and src.size(1) == other.size(1))
     _mismatch(src.size(2) == window_size * 2 + 1)
-    return band_n(src, other, window_size)
+    return band_n(src, other, window_size, out=out)
 
 
 def unwindow_matmul_backward(src, other, window_size, grad_output, need=(True, True), out=None):
@@ -167,6 +167,110 @@ def unwindow_matmul_backward(src, other, window_size, grad_output, need=(True, T
     ga = band_nt(grad_output, other, window_size) if need[0] else None
     gv = band_t(src, grad_output, window_size) if need[1] else None
     return ga, gv
+
+
+# ---- leading dimensions ---------------------------------------------------------------------------
+# The reference flattens the leading dimensions with `reshape` (window_matmul/window_matmul.py:36-37, 72-73), which
+# silently COPIES an operand whose leading dimensions cannot be merged, e.g. the (B, H, M, N) view of a (B, M, H*N)
+# projection.  Here such operands are consumed where they are: the outermost dimensions are looped over until what
+# remains of every operand is a view (batch, rows, cols) with element strides, which the kernels take directly.
+
+
+def _viewable3(t: torch.Tensor) -> bool:
+    try:
+        t.view(-1, t.shape[-2], t.shape[-1])
+        return True
+    except RuntimeError:
+        return False
+
+
+def split_depth(*tensors: torch.Tensor) -> int:
+    """Smallest number of outermost dimensions to loop over so that the rest of every tensor is a 3-D view."""
+    lead = tensors[0].dim() - 2
+    for d in range(lead + 1):
+        if all(_viewable3(t[(0,) * d] if d and t.numel() else t) for t in tensors):
+            return d
+    return lead
+
+
+def _slices(depth: int, shape) -> list:
+    import itertools
+
+    return list(itertools.product(*[range(n) for n in shape[:depth]]))
+
+
+def _v3(t: torch.Tensor, idx) -> torch.Tensor:
+    s = t[idx] if idx else t
+    return s.view(-1, s.shape[-2], s.shape[-1])
+
+
+class _StridedWindowMatmulFunc(torch.autograd.Function):
+    """WindowMatmulFunc for operands whose leading dimensions do not merge: same kernels, one call per outer index."""
+
+    @staticmethod
+    @torch.amp.custom_fwd(device_type="cuda", cast_inputs=torch.float16)
+    def forward(ctx, inp, other, window_size, depth):
+        _require_cuda(inp, other)
+        *dims, M, Nh = inp.shape
+        out = torch.empty((*dims, M, 2 * window_size + 1), dtype=inp.dtype, device=inp.device)
+        for idx in _slices(depth, inp.shape):
+            window_matmul_forward(_v3(inp, idx), _v3(other, idx), window_size, out=_v3(out, idx))
+        ctx.save_for_backward(inp, other)
+        ctx.depth = depth
+        return out
+
+    @staticmethod
+    @torch.amp.custom_bwd(device_type="cuda")
+    def backward(ctx, grad_output):
+        inp, other = ctx.saved_tensors
+        window_size = grad_output.shape[-1] // 2
+        grad_output = grad_output.contiguous()
+        need = tuple(ctx.needs_input_grad[:2])
+        gq = torch.empty(inp.shape, dtype=inp.dtype, device=inp.device) if need[0] else None
+        gkt = torch.empty(inp.shape, dtype=inp.dtype, device=inp.device) if need[1] else None
+        for idx in _slices(ctx.depth, inp.shape):
+            if need[0] and need[1]:
+                window_matmul_backward(_v3(inp, idx), _v3(other, idx), window_size, _v3(grad_output, idx),
+                                       out=(_v3(gq, idx), _v3(gkt, idx)))
+            elif need[0]:
+                band_n(_v3(grad_output, idx), _addressable(_v3(other, idx).transpose(-1, -2)), window_size, out=_v3(gq, idx))
+            elif need[1]:
+                band_t(_v3(grad_output, idx), _addressable(_v3(inp, idx)), window_size, out=_v3(gkt, idx))
+        return gq, (gkt.transpose(-1, -2) if need[1] else None), None, None
+
+
+class _StridedUnwindowMatmulFunc(torch.autograd.Function):
+    """UnwindowMatmulFunc for operands whose leading dimensions do not merge."""
+
+    @staticmethod
+    @torch.amp.custom_fwd(device_type="cuda", cast_inputs=torch.float16)
+    def forward(ctx, inp, other, window_size, depth):
+        _require_cuda(inp, other)
+        out = torch.empty(other.shape, dtype=other.dtype, device=other.device)
+        for idx in _slices(depth, other.shape):
+            unwindow_matmul_forward(_v3(inp, idx), _v3(other, idx), window_size, out=_v3(out, idx))
+        ctx.save_for_backward(inp, other)
+        ctx.depth = depth
+        return out
+
+    @staticmethod
+    @torch.amp.custom_bwd(device_type="cuda")
+    def backward(ctx, grad_output):
+        inp, other = ctx.saved_tensors
+        window_size = inp.shape[-1] // 2
+        need = tuple(ctx.needs_input_grad[:2])
+        ga = torch.empty(inp.shape, dtype=inp.dtype, device=inp.device) if need[0] else None
+        gv = torch.empty(other.shape, dtype=other.dtype, device=other.device) if need[1] else None
+        depth = max(ctx.depth, split_depth(grad_output))
+        for idx in _slices(depth, other.shape):
+            a3, v3, g3 = _v3(inp, idx), _v3(other, idx), _v3(grad_output, idx)
+            if need[0] and need[1]:
+                unwindow_matmul_backward(a3, v3, window_size, g3, out=(_v3(ga, idx), _v3(gv, idx)))
+            elif need[0]:
+                band_nt(_addressable(g3), _addressable(v3), window_size, out=_v3(ga, idx))
+            elif need[1]:
+                band_t(a3.contiguous(), _addressable(g3), window_size, out=_v3(gv, idx))
+        return ga, gv, None, None
 
 
 # ---- autograd nodes and the public functions ------------------------------------------------------
@@ -199,6 +303,10 @@ def window_matmul(inp: torch.Tensor, other: torch.Tensor, window_size: int) -> t
     if not window_size:
         return (inp * other.transpose(-1, -2)).sum(dim=-1, keepdim=True)
     *dims, seq_len, hidden_dim = inp.shape
+    if inp.is_cuda and other.is_cuda and other.shape == (*dims, hidden_dim, seq_len):
+        depth = split_depth(inp, other)
+        if depth:   # leading dimensions that do not merge: no copy, one call per outer index
+            return _StridedWindowMatmulFunc.apply(inp, other, window_size, depth)
     inp = inp.reshape(-1, seq_len, hidden_dim)
     other = other.reshape(-1, hidden_dim, seq_len)
     out = WindowMatmulFunc.apply(inp, other, window_size)
@@ -233,6 +341,10 @@ def unwindow_matmul(inp: torch.Tensor, other: torch.Tensor, window_size: int) ->
     if not window_size:
         return inp * other
     *dims, seq_len, hidden_dim = other.shape
+    if inp.is_cuda and other.is_cuda and inp.shape == (*dims, seq_len, window_size * 2 + 1):
+        depth = split_depth(inp, other)
+        if depth:
+            return _StridedUnwindowMatmulFunc.apply(inp, other, window_size, depth)
     inp = inp.reshape(-1, seq_len, window_size * 2 + 1)
     other = other.reshape(-1, seq_len, hidden_dim)
     out = UnwindowMatmulFunc.apply(inp, other, window_size)
