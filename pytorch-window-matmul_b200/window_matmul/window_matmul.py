@@ -176,9 +176,16 @@ def unwindow_matmul_backward(src, other, window_size, grad_output, need=(True, T
 # remains of every operand is a view (batch, rows, cols) with element strides, which the kernels take directly.
 
 
+def _lead(t: torch.Tensor) -> int:
+    n = 1
+    for d in t.shape[:-2]:
+        n *= d
+    return n
+
+
 def _viewable3(t: torch.Tensor) -> bool:
     try:
-        t.view(-1, t.shape[-2], t.shape[-1])
+        t.view(_lead(t), t.shape[-2], t.shape[-1])   # (an explicit size: -1 is ambiguous for empty tensors)
         return True
     except RuntimeError:
         return False
@@ -201,7 +208,7 @@ def _slices(depth: int, shape) -> list:
 
 def _v3(t: torch.Tensor, idx) -> torch.Tensor:
     s = t[idx] if idx else t
-    return s.view(-1, s.shape[-2], s.shape[-1])
+    return s.view(_lead(s), s.shape[-2], s.shape[-1])
 
 
 class _StridedWindowMatmulFunc(torch.autograd.Function):
@@ -307,8 +314,8 @@ def window_matmul(inp: torch.Tensor, other: torch.Tensor, window_size: int) -> t
         depth = split_depth(inp, other)
         if depth:   # leading dimensions that do not merge: no copy, one call per outer index
             return _StridedWindowMatmulFunc.apply(inp, other, window_size, depth)
-    inp = inp.reshape(-1, seq_len, hidden_dim)
-    other = other.reshape(-1, hidden_dim, seq_len)
+    inp = inp.reshape(_lead(inp), seq_len, hidden_dim)        # (-1 would be ambiguous for an empty sequence)
+    other = other.reshape(_lead(other), hidden_dim, seq_len)
     out = WindowMatmulFunc.apply(inp, other, window_size)
     out = out.reshape(*dims, seq_len, window_size * 2 + 1)
     return out
@@ -345,8 +352,8 @@ def unwindow_matmul(inp: torch.Tensor, other: torch.Tensor, window_size: int) ->
         depth = split_depth(inp, other)
         if depth:
             return _StridedUnwindowMatmulFunc.apply(inp, other, window_size, depth)
-    inp = inp.reshape(-1, seq_len, window_size * 2 + 1)
-    other = other.reshape(-1, seq_len, hidden_dim)
+    inp = inp.reshape(_lead(inp), seq_len, window_size * 2 + 1)
+    other = other.reshape(_lead(other), seq_len, hidden_dim)
     out = UnwindowMatmulFunc.apply(inp, other, window_size)
     out = out.reshape(*dims, seq_len, hidden_dim)
     return out

@@ -451,3 +451,36 @@ def test_host_pipeline_matches_direct_calls(wm):
     assert torch.equal(a_h, a_d.cpu()) and torch.equal(o_h, o_d.cpu())
     with pytest.raises(RuntimeError, match="host tensors"):
         batched_host_call(fn, [q.cuda(), kt, v])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_empty_single_row_and_window_wider_than_the_sequence(wm, dtype):
+    """Edge sizes through the public operators: no batch entries, no rows, one row, a window several times the
+    sequence length (every band slot but a few is out of sequence).  Forward and backward, against the oracle."""
+    import window_matmul as pkg
+
+    for B, M, Nn, w in [(0, 8, 4, 2), (2, 0, 4, 2)]:
+        q = torch.zeros(B, M, Nn, dtype=dtype, device="cuda", requires_grad=True)
+        k = torch.zeros(B, Nn, M, dtype=dtype, device="cuda", requires_grad=True)
+        a = pkg.window_matmul(q, k, w)
+        assert a.shape == (B, M, 2 * w + 1)
+        o = pkg.unwindow_matmul(a, torch.zeros(B, M, Nn, dtype=dtype, device="cuda"), w)
+        assert o.shape == (B, M, Nn)
+        o.sum().backward()
+        assert q.grad.shape == q.shape and k.grad.shape == k.shape
+    for B, M, Nn, w in [(3, 1, 8, 3), (2, 5, 64, 16), (1, 8, 32, 64)]:
+        d = {key: H.round_to(val, dtype) for key, val in H.rand_inputs(B, M, Nn, w, seed=B + M + w).items()}
+        want = H.oracle.chain_fwd_bwd(d["q"], np.ascontiguousarray(d["kt"].transpose(0, 2, 1)), d["v"], w, d["g_out"])
+        q, kt, v = (H.to_dev(d[key], dtype).requires_grad_(True) for key in ("q", "kt", "v"))
+        a = pkg.window_matmul(q, kt.transpose(-1, -2), w)
+        a.retain_grad()
+        o = pkg.unwindow_matmul(a, v, w)
+        o.backward(H.to_dev(d["g_out"], dtype))
+        got = (a, o, q.grad, kt.grad.transpose(1, 2), a.grad, v.grad)
+        for name, x, y in zip(("a", "o", "gq", "gk", "ga", "gv"), got, want):
+            if dtype == torch.float32:
+                H.assert_lowp_close(x, y, "%s %s" % (name, (B, M, Nn, w)), rel=2e-5)
+            else:
+                H.assert_lowp_close(x, y, "%s %s" % (name, (B, M, Nn, w)), rel=4e-2 if name != "a" else 1e-2)
+        outside = H.out_of_sequence_mask(M, w)
+        assert (a.detach().float().cpu().numpy()[:, outside] == 0).all() and (a.grad.float().cpu().numpy()[:, outside] == 0).all()
