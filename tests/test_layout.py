@@ -59,3 +59,40 @@ def test_head_split_views_give_the_results_of_contiguous_operands(dtype):
     assert n_contig == 1 and n_strided == B
     for name, x, y in zip(("a", "o", "grad_q_proj", "grad_k_proj", "grad_v_proj"), got, want):
         assert torch.equal(x, y), name
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,dilation", [(torch.float32, 2), (torch.bfloat16, 4)])
+def test_dilated_windows_by_views(dtype, dilation):
+    """Dilated windowed attention (scores, masked softmax, values; forward and backward) from the residue-class views
+    against the dense formulation with the dilated band mask, in float64."""
+    from window_matmul import window_softmax
+    from window_matmul.dilated import dilated_unwindow_matmul, dilated_window_matmul
+
+    B, M, Nn, w, d = 2, 512, 64, 16, dilation
+    g = torch.Generator().manual_seed(7)
+    q, k, v, go = (torch.randn(B, M, Nn, generator=g).to(dtype) for _ in range(4))
+    scale = 1.0 / math.sqrt(Nn)
+
+    qd, kd, vd = (t.double().requires_grad_(True) for t in (q, k, v))
+    i = torch.arange(M)
+    diff = i[None, :] - i[:, None]
+    allowed = (diff % d == 0) & (diff.abs() <= w * d)
+    dense = torch.softmax((qd @ kd.transpose(-1, -2) * scale).masked_fill(~allowed, float("-inf")), -1) @ vd
+    dense.backward(go.double())
+
+    qc, kc, vc = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    band = dilated_window_matmul(qc, kc.transpose(-1, -2), w, d)
+    assert band.shape == (B, d, M // d, 2 * w + 1)
+    # entry [r, t, j] = q[t d + r] . k[(t + j - w) d + r]
+    r, t, j = 1, 5, w + 3
+    want = (q[0, t * d + r].double() * k[0, (t + j - w) * d + r].double()).sum()
+    assert abs(float(band.detach()[0, r, t, j]) - float(want)) <= 2e-2 * (abs(float(want)) + 1)
+    out = dilated_unwindow_matmul(window_softmax(band, scale, True), vc, w, d)
+    out.backward(go.cuda())
+    torch.cuda.synchronize()
+    rel = 1e-4 if dtype == torch.float32 else 4e-2
+    import helpers as H
+
+    for name, got, ref in (("o", out, dense), ("gq", qc.grad, qd.grad), ("gk", kc.grad, kd.grad), ("gv", vc.grad, vd.grad)):
+        H.assert_lowp_close(got, ref.detach().numpy(), name, rel=rel)
