@@ -48,7 +48,7 @@
 extern "C" {
 #endif
 
-#define WMM_ABI_VERSION 1
+#define WMM_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define WMM_API __attribute__((visibility("default")))
@@ -195,8 +195,9 @@ typedef struct wmm_halo_buffer {
 
 /* Flag words of the hand-shake.  `mine`, `lower`, `upper`: this rank's and the neighbours' blocks of at least 4
  * 32-bit words in memory every neighbour can read AND write (word 0: ready epoch, word 1 / 2: acknowledgement written
- * by the lower / upper neighbour), zero before the first call; NULL for a missing neighbour.  `counters`: 2 words of
- * plain device memory of this rank, zero before the first call. */
+ * by the lower / upper neighbour), zero before the first call; NULL for a missing neighbour.  `counters`: 4 words of
+ * plain device memory of this rank, zero before the first call (word 0: exchanges completed; words 1-3: scratch of the
+ * running launch). */
 typedef struct wmm_halo_flags {
   unsigned *mine;
   unsigned *lower;
@@ -210,8 +211,10 @@ typedef struct wmm_halo_flags {
  *   accumulate != 0: this rank's first `window` own rows += the lower neighbour's upper margin, its last `window` own rows
  *                    += the upper neighbour's lower margin (partial grad_K / grad_V rows after the backward contractions;
  *                    needs rows >= 2*window).
- * Every rank of the sequence group must issue the same sequence of these calls.  The kernel waits (at most ~1 s per
- * wait) for the neighbours' kernels of the same call; a wait that runs out sets bit 5 of wmm_device_status().  The
+ * Every rank of the sequence group must issue the same sequence of these calls.  The kernel waits for the neighbours'
+ * kernels of the same call: at most ~1 s for a neighbour to start (a side whose neighbour does not show up is skipped, the
+ * other side is still served) and at most ~3 s for a neighbour to finish reading this rank's rows; a wait that runs out
+ * sets bit 5 of wmm_device_status().  The
  * reference has no multi-GPU code; this replaces the send/recv pairs of a host communication library on that path. */
 WMM_API int wmm_halo_pull(const wmm_halo_buffer *buffers, int count, const wmm_halo_flags *flags, int batch, int rows,
                           int cols, int window, int dtype, int accumulate, void *stream);

@@ -244,8 +244,8 @@ int wmm_halo_pull(const wmm_halo_buffer *buffers, int count, const wmm_halo_flag
       return fail(WMM_ERR_NULL, "buffer %d and the flags disagree on which neighbours exist", i);
   }
   int launches = 0;
-  cudaError_t err = wmm::launch_halo_pull(buffers, count, *flags, batch, rows, cols, window, dtype, accumulate != 0,
-                                          (cudaStream_t)stream, &launches);
+  cudaError_t err = wmm::launch_halo_pull(buffers, count, *flags, flags->counters, flags->counters + 1, batch, rows, cols, window,
+                                          dtype, accumulate != 0, (cudaStream_t)stream, &launches);
   g_launches.fetch_add((uint64_t)launches, std::memory_order_relaxed);
   if (err != cudaSuccess) return fail(WMM_ERR_CUDA, "CUDA error launching the halo exchange: %s", cudaGetErrorString(err));
   return WMM_OK;

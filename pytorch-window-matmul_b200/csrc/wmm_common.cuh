@@ -49,8 +49,10 @@ cudaError_t launch_band_softmax(bool backward, const void *in, const void *in2, 
                                 int dtype, float scale, bool mask, cudaStream_t stream, int *launches);
 
 // Neighbour exchange of halo rows through peer memory (wmm_halo.cu).
-cudaError_t launch_halo_pull(const wmm_halo_buffer *bufs, int count, const wmm_halo_flags &flags, int batch, int rows,
-                             int cols, int window, int dtype, bool accumulate, cudaStream_t stream, int *launches);
+// `epoch_word`: one local word counting the completed exchanges; `scratch`: three local words (CTAs done, go word per side).
+cudaError_t launch_halo_pull(const wmm_halo_buffer *bufs, int count, const wmm_halo_flags &flags, unsigned *epoch_word,
+                             unsigned *scratch, int batch, int rows, int cols, int window, int dtype, bool accumulate,
+                             cudaStream_t stream, int *launches);
 
 // Launchers describe a failure (which step, which driver code) here; the API layer appends it to the
 // error string of the calling thread.

@@ -8,14 +8,22 @@
 //                                neighbour's first w own rows            (forward halo of K^T and V rows)
 //   reduction  (accumulate = 1): my first w own rows += the lower neighbour's upper margin, my last w own rows += the
 //                                upper neighbour's lower margin          (reverse halo of partial grad_K / grad_V rows)
-// Plain peer loads (16 bytes per thread and access), local stores: no TMA, no multicast.
+// Plain peer loads (16 bytes per access, several in flight per thread), local stores: no TMA, no multicast.
 //
 // Hand-shake, per launch, with an epoch e that every rank counts in step (all ranks issue the same sequence of these
-// launches): (1) a rank publishes ready = e when its kernel starts (everything earlier in its stream is complete, so its
-// rows are final); (2) a CTA copies from a neighbour only after it has seen that neighbour's ready >= e; (3) when all
-// CTAs are done the rank writes ack = e into both neighbours' flag blocks and waits for their acks, so nothing later in
-// its own stream can overwrite rows a neighbour is still reading.  Every wait is bounded by wall clock (1 s): a wait
-// that runs out sets the status word (bit 5) and the kernel returns without hanging.
+// launches).  The two sides (lower / upper neighbour) are independent of each other:
+//   (1) the rank publishes ready = e when its kernel starts (everything earlier in its stream is complete, so its rows
+//       are final);
+//   (2) CTA 0 alone polls the neighbours' ready words over the link, one thread per side, for at most kReadyWaitNs, and
+//       publishes the verdict of each side in a LOCAL go word; the other CTAs poll those local words.  A side whose
+//       neighbour did not show up in time is skipped by every CTA (each one raises the status bit itself); the other side
+//       is still copied;
+//   (3) when all CTAs are done the rank writes ack = e into both neighbours' flag blocks, whether it copied from them or
+//       gave up on them, and then waits for their acks, so that nothing later in its own stream can overwrite rows a
+//       neighbour is still reading.  The ack wait (kAckWaitNs) is longer than a neighbour's ready wait plus its copy, so
+//       a rank whose OTHER neighbour is absent still acknowledges in time: only the ranks next to an absent one report
+//       a time-out.
+// Every wait is bounded by wall clock: a wait that runs out sets the status word (bit 5) and the kernel returns.
 #include "wmm_common.cuh"
 
 namespace wmm {
@@ -23,8 +31,11 @@ namespace {
 
 constexpr int kHaloThreads = 256;
 constexpr int kHaloMaxBuffers = 4;
+constexpr int kHaloUnroll = 4;           // independent 16-byte peer loads in flight per thread
 constexpr unsigned long long ST_HALO_TIMEOUT = 1ull << 5;
-constexpr unsigned long long kHaloWaitNs = 1000ull * 1000ull * 1000ull;
+constexpr unsigned long long kReadyWaitNs = 1000ull * 1000ull * 1000ull;
+constexpr unsigned long long kGoWaitNs = 1500ull * 1000ull * 1000ull;     // local wait for CTA 0's verdict
+constexpr unsigned long long kAckWaitNs = 3000ull * 1000ull * 1000ull;
 
 struct HaloArgs {
   void *local[kHaloMaxBuffers];
@@ -40,7 +51,8 @@ struct HaloArgs {
   // flag words: [0] ready, [1] ack written by the lower neighbour, [2] ack written by the upper neighbour
   unsigned *mine;
   unsigned *lower_flags, *upper_flags;   // peer pointers or NULL
-  unsigned *counters;                    // local: [0] epoch, [1] CTAs done
+  unsigned *epoch_word;                  // local: epochs completed so far
+  unsigned *scratch;                     // local: [0] CTAs done, [1] go word of the lower side, [2] of the upper side
   unsigned long long *status;
 };
 
@@ -52,19 +64,37 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
 __device__ __forceinline__ void st_release_sys(unsigned *p, unsigned v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+__device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned *p) {
+  unsigned v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu(unsigned *p, unsigned v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ unsigned long long timer_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
 // waits until *p >= want (epochs only grow); false if the wait ran out
-__device__ __forceinline__ bool wait_at_least(const unsigned *p, unsigned want) {
+__device__ __forceinline__ bool wait_at_least(const unsigned *p, unsigned want, unsigned long long limit_ns) {
   if ((int)(ld_acquire_sys(p) - want) >= 0) return true;
   const unsigned long long t0 = timer_ns();
   for (;;) {
     if ((int)(ld_acquire_sys(p) - want) >= 0) return true;
-    if (timer_ns() - t0 > kHaloWaitNs) return false;
+    if (timer_ns() - t0 > limit_ns) return false;
     __nanosleep(200);
+  }
+}
+// A go word holds 2 * epoch + (1 if the neighbour was ready in time).  Returns that bit, 0 also if the wait ran out.
+__device__ __forceinline__ bool wait_go(const unsigned *p, unsigned e) {
+  const unsigned long long t0 = timer_ns();
+  for (;;) {
+    const unsigned v = ld_acquire_gpu(p);
+    if ((int)((v >> 1) - e) >= 0) return (v & 1u) != 0;
+    if (timer_ns() - t0 > kGoWaitNs) return false;
+    __nanosleep(100);
   }
 }
 
@@ -79,72 +109,98 @@ template <typename T> __device__ __forceinline__ uint4 add16(uint4 a, uint4 b) {
 
 template <typename T>
 __global__ void __launch_bounds__(kHaloThreads) halo_pull_kernel(const HaloArgs a) {
-  __shared__ int ok_s;
-  const unsigned e = *reinterpret_cast<volatile unsigned *>(a.counters) + 1u;
-  if (threadIdx.x == 0) {
+  __shared__ int ok_s[2];
+  __shared__ int last_s;
+  const unsigned e = *reinterpret_cast<volatile unsigned *>(a.epoch_word) + 1u;
+  // threads 0 and 32 look after the lower and the upper side
+  if (threadIdx.x == 0 || threadIdx.x == 32) {
+    const int side = threadIdx.x >> 5;
+    const unsigned *peer = side == 0 ? a.lower_flags : a.upper_flags;
+    bool ok = false;
     if (blockIdx.x == 0) {
-      __threadfence_system();
-      st_release_sys(a.mine, e);   // my rows are final: everything earlier in this stream has completed
+      if (side == 0) {
+        __threadfence_system();
+        st_release_sys(a.mine, e);   // my rows are final: everything earlier in this stream has completed
+      }
+      if (peer) ok = wait_at_least(peer, e, kReadyWaitNs);
+      st_release_gpu(a.scratch + 1 + side, 2u * e + (ok ? 1u : 0u));   // the verdict on this side, for the other CTAs
+    } else if (peer) {
+      ok = wait_go(a.scratch + 1 + side, e);
     }
-    bool ok = true;
-    if (a.lower_flags) ok = wait_at_least(a.lower_flags, e);
-    if (ok && a.upper_flags) ok = wait_at_least(a.upper_flags, e);
-    ok_s = ok ? 1 : 0;
+    ok_s[side] = ok ? 1 : 0;
+    if (peer && !ok && a.status) atomicOr(a.status, ST_HALO_TIMEOUT);   // every CTA reports the share it skips
   }
   __syncthreads();
-  const bool ok = ok_s != 0;
-  if (ok) {
-    // work items: (buffer, side, batch entry, vector of the strip)
-    const long long per_side = (long long)a.batch * a.strip_vecs;
-    const long long total = (long long)a.count * 2 * per_side;
-    for (long long it = (long long)blockIdx.x * kHaloThreads + threadIdx.x; it < total; it += (long long)gridDim.x * kHaloThreads) {
-      const int t = (int)(it / (2 * per_side));
-      const long long r = it % (2 * per_side);
-      const int side = (int)(r / per_side);   // 0: lower neighbour, 1: upper neighbour
-      const long long q = r % per_side;
-      const long long b = q / a.strip_vecs, v = q % a.strip_vecs;
-      const uint4 *src = static_cast<const uint4 *>(side == 0 ? a.lower[t] : a.upper[t]);
-      if (!src) continue;
-      uint4 *dst = static_cast<uint4 *>(a.local[t]);
-      long long s_off, d_off;
-      if (!a.accumulate) {
-        // lower: neighbour's last w own rows (they end where its upper margin starts) -> my lower margin
-        // upper: neighbour's first w own rows (they start after its lower margin)     -> my upper margin
-        s_off = b * a.row_vecs + (side == 0 ? a.own_vecs - a.strip_vecs : a.strip_vecs) + v;
-        d_off = b * a.row_vecs + (side == 0 ? 0 : a.own_vecs) + v;
-        dst[d_off] = __ldcg(src + s_off);
-      } else {
-        // lower: neighbour's upper margin -> added to my first w own rows; upper: neighbour's lower margin -> my last w
-        s_off = b * a.row_vecs + (side == 0 ? a.own_vecs : 0) + v;
-        d_off = b * a.row_vecs + (side == 0 ? a.strip_vecs : a.own_vecs - a.strip_vecs) + v;
-        dst[d_off] = add16<T>(dst[d_off], __ldcg(src + s_off));
+
+  // work items of one side: (buffer, batch entry, vector of the strip); kHaloUnroll of them in flight per thread
+  const long long per_buf = (long long)a.batch * a.strip_vecs;
+  const long long per_side = (long long)a.count * per_buf;
+  for (int side = 0; side < 2; ++side) {
+    if (!ok_s[side]) continue;
+    for (long long it0 = (long long)blockIdx.x * (kHaloThreads * kHaloUnroll) + threadIdx.x; it0 < per_side;
+         it0 += (long long)gridDim.x * (kHaloThreads * kHaloUnroll)) {
+      uint4 val[kHaloUnroll], own[kHaloUnroll];
+      uint4 *dst[kHaloUnroll];
+#pragma unroll
+      for (int u = 0; u < kHaloUnroll; ++u) {
+        const long long it = it0 + (long long)u * kHaloThreads;
+        dst[u] = nullptr;
+        if (it >= per_side) continue;
+        const int t = (int)(it / per_buf);
+        const long long q = it % per_buf;
+        const long long b = q / a.strip_vecs, v = q % a.strip_vecs;
+        const uint4 *src = static_cast<const uint4 *>(side == 0 ? a.lower[t] : a.upper[t]);
+        long long s_off, d_off;
+        if (!a.accumulate) {
+          // lower: neighbour's last w own rows (they end where its upper margin starts) -> my lower margin
+          // upper: neighbour's first w own rows (they start after its lower margin)     -> my upper margin
+          s_off = b * a.row_vecs + (side == 0 ? a.own_vecs - a.strip_vecs : a.strip_vecs) + v;
+          d_off = b * a.row_vecs + (side == 0 ? 0 : a.own_vecs) + v;
+        } else {
+          // lower: neighbour's upper margin -> added to my first w own rows; upper: neighbour's lower margin -> my last w
+          s_off = b * a.row_vecs + (side == 0 ? a.own_vecs : 0) + v;
+          d_off = b * a.row_vecs + (side == 0 ? a.strip_vecs : a.own_vecs - a.strip_vecs) + v;
+        }
+        dst[u] = static_cast<uint4 *>(a.local[t]) + d_off;
+        val[u] = __ldcg(src + s_off);
+        if (a.accumulate) own[u] = *dst[u];
       }
+#pragma unroll
+      for (int u = 0; u < kHaloUnroll; ++u)
+        if (dst[u]) *dst[u] = a.accumulate ? add16<T>(own[u], val[u]) : val[u];
     }
   }
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
-    const unsigned prev = atomicAdd(a.counters + 1, 1u);
-    if (prev == gridDim.x - 1) {   // the last CTA of this launch
-      a.counters[1] = 0;
-      bool fine = ok;
-      __threadfence_system();
-      // my reads of the neighbours' rows are done: tell them; then wait until they are done with mine
-      if (a.lower_flags) st_release_sys(a.lower_flags + 2, e);   // I am the lower neighbour's UPPER neighbour
-      if (a.upper_flags) st_release_sys(a.upper_flags + 1, e);
-      if (a.lower_flags) fine = wait_at_least(a.mine + 1, e) && fine;
-      if (a.upper_flags) fine = wait_at_least(a.mine + 2, e) && fine;
-      a.counters[0] = e;
-      if (!fine && a.status) atomicOr(a.status, ST_HALO_TIMEOUT);
-      __threadfence();
+    last_s = atomicAdd(a.scratch, 1u) == gridDim.x - 1 ? 1 : 0;   // the last CTA of this launch closes the hand-shake
+  }
+  __syncthreads();
+  if (!last_s) return;
+  if (threadIdx.x == 0 || threadIdx.x == 32) {
+    const int side = threadIdx.x >> 5;
+    unsigned *peer = side == 0 ? a.lower_flags : a.upper_flags;
+    if (side == 0) a.scratch[0] = 0;
+    __threadfence_system();
+    if (peer) {
+      // my reads of this neighbour's rows are done (or given up): tell it, then wait until it is done with mine.
+      // (I am the lower neighbour's UPPER neighbour and the upper neighbour's LOWER one.)
+      st_release_sys(peer + (side == 0 ? 2 : 1), e);
+      if (!wait_at_least(a.mine + 1 + side, e, kAckWaitNs) && a.status) atomicOr(a.status, ST_HALO_TIMEOUT);
     }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    *a.epoch_word = e;
+    __threadfence();
   }
 }
 
 }  // namespace
 
-cudaError_t launch_halo_pull(const wmm_halo_buffer *bufs, int count, const wmm_halo_flags &flags, int batch, int rows,
-                             int cols, int window, int dtype, bool accumulate, cudaStream_t stream, int *launches) {
+cudaError_t launch_halo_pull(const wmm_halo_buffer *bufs, int count, const wmm_halo_flags &flags, unsigned *epoch_word,
+                             unsigned *scratch, int batch, int rows, int cols, int window, int dtype, bool accumulate,
+                             cudaStream_t stream, int *launches) {
   const size_t e = dtype == WMM_F32 ? 4 : dtype == WMM_F64 ? 8 : 2;
   HaloArgs a{};
   a.count = count;
@@ -162,10 +218,11 @@ cudaError_t launch_halo_pull(const wmm_halo_buffer *bufs, int count, const wmm_h
   a.mine = flags.mine;
   a.lower_flags = flags.lower;
   a.upper_flags = flags.upper;
-  a.counters = flags.counters;
+  a.epoch_word = epoch_word;
+  a.scratch = scratch;
   a.status = device_status_word();
-  const long long total = (long long)count * 2 * batch * a.strip_vecs;
-  long long blocks = (total + kHaloThreads * 8 - 1) / (kHaloThreads * 8);
+  const long long per_side = (long long)count * batch * a.strip_vecs;
+  long long blocks = (per_side + kHaloThreads * kHaloUnroll - 1) / (kHaloThreads * kHaloUnroll);
   if (blocks < 1) blocks = 1;
   if (blocks > 128) blocks = 128;
   switch (dtype) {

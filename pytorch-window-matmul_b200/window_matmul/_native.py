@@ -92,8 +92,8 @@ def _load():
     lib.wmm_band_softmax.argtypes = [vp, vp, P(Geometry), i32, ctypes.c_float, u32, vp]
     lib.wmm_band_softmax_bwd.restype = i32
     lib.wmm_band_softmax_bwd.argtypes = [vp, vp, vp, P(Geometry), i32, ctypes.c_float, u32, vp]
-    if lib.wmm_version() != 1:
-        raise RuntimeError("window_matmul: %s has ABI version %d, expected 1" % (LIB_PATH, lib.wmm_version()))
+    if lib.wmm_version() != 2:
+        raise RuntimeError("window_matmul: %s has ABI version %d, expected 2" % (LIB_PATH, lib.wmm_version()))
     return lib
 
 

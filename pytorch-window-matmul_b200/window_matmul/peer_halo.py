@@ -43,7 +43,7 @@ class PeerHalo:
         self.store.zero_()
         self.flags = symm_mem.empty((64,), dtype=torch.int32, device=self.device)
         self.flags.zero_()
-        self.counters = torch.zeros(2, dtype=torch.int32, device=self.device)
+        self.counters = torch.zeros(4, dtype=torch.int32, device=self.device)
         torch.cuda.synchronize(self.device)
         hdl = symm_mem.rendezvous(self.store, self.group)
         fhdl = symm_mem.rendezvous(self.flags, self.group)

@@ -51,27 +51,26 @@ def _neighbours(group) -> Tuple[int, int, Optional[int], Optional[int]]:
     return rank, world, lo, hi
 
 
-_HALO_STORAGE = {}  # data_ptr of a local view -> (extended buffer, window); see alloc_with_halo
-
-
 def alloc_with_halo(batch: int, rows: int, cols: int, window: int, dtype, device):
     """Storage for a sequence shard WITH room for its halos: returns (local, extended) where `extended` is a
     (batch, rows + 2w, cols) buffer and `local` = extended[:, w:w+rows] is the view to keep the shard's rows in.
-    exchange_halo() on such a view fills the margins in place instead of copying the shard into a new buffer."""
+    exchange_halo() on such a view fills the margins in place instead of copying the shard into a new buffer
+    (the view itself remembers the buffer it was cut from: nothing is registered anywhere)."""
     ext = torch.zeros((batch, rows + 2 * window, cols), dtype=dtype, device=device)
     local = ext[:, window:window + rows]
-    _HALO_STORAGE[local.data_ptr()] = (ext, window)
     return local, ext
 
 
 def _extended(x: torch.Tensor, window: int) -> torch.Tensor:
-    """The (B, Ml + 2w, N) buffer whose middle rows are x: x's own storage if it came from alloc_with_halo(),
-    else a new zeroed buffer with x copied in."""
+    """The (B, Ml + 2w, N) buffer whose middle rows are x: the tensor x is a view of if x was cut from such a buffer
+    the way alloc_with_halo() does, else a new zeroed buffer with x copied in."""
     B, Ml, N = x.shape
-    held = _HALO_STORAGE.get(x.data_ptr())
-    if held is not None and held[1] == window and held[0].shape == (B, Ml + 2 * window, N) and held[0].dtype == x.dtype \
-            and x.stride() == held[0][:, window:window + Ml].stride():
-        return held[0]
+    held = x._base
+    if held is not None and held.dim() == 3 and held.shape == (B, Ml + 2 * window, N) and held.dtype == x.dtype \
+            and held.is_contiguous():
+        mid = held[:, window:window + Ml]
+        if mid.data_ptr() == x.data_ptr() and mid.stride() == x.stride():
+            return held
     ext = x.new_zeros((B, Ml + 2 * window, N))
     ext[:, window:window + Ml] = x
     return ext

@@ -25,6 +25,14 @@ def _check(t: torch.Tensor) -> None:
         raise RuntimeError("Input mismatch")
 
 
+def _check_out(out: torch.Tensor, like: torch.Tensor) -> torch.Tensor:
+    """A caller-supplied output is written as a contiguous, 16-byte aligned band of `like`'s shape and dtype."""
+    if not (isinstance(out, torch.Tensor) and out.shape == like.shape and out.dtype == like.dtype
+            and out.device == like.device and out.is_contiguous() and out.data_ptr() % 16 == 0):
+        raise RuntimeError("Input mismatch")
+    return out
+
+
 def band_softmax(scores, scale=1.0, mask=True, *, other_off=0, seq=None, other_rows=None, out=None):
     """Forward on a (B,M,2w+1) tensor.  `other_off`, `seq`, `other_rows` as in the three primitives: slot j of row i
     is in sequence iff seq[0] <= i + j - w + other_off < seq[1] (a sequence shard passes its halo geometry)."""
@@ -32,7 +40,7 @@ def band_softmax(scores, scale=1.0, mask=True, *, other_off=0, seq=None, other_r
     scores = scores.contiguous()
     B, M, W = scores.shape
     w = (W - 1) // 2
-    probs = torch.empty_like(scores) if out is None else out
+    probs = torch.empty_like(scores) if out is None else _check_out(out, scores)
     g = N.geometry(B, M, 0, w, M if other_rows is None else other_rows, other_off, seq)
     with torch.cuda.device(scores.device):
         N.check(N.lib.wmm_band_softmax(scores.data_ptr(), probs.data_ptr(), g, N.dtype_code(scores), float(scale),
@@ -49,7 +57,7 @@ def band_softmax_backward(probs, grad_probs, scale=1.0, mask=True, *, other_off=
     probs, grad_probs = probs.contiguous(), grad_probs.contiguous()
     B, M, W = probs.shape
     w = (W - 1) // 2
-    grad_scores = torch.empty_like(probs) if out is None else out
+    grad_scores = torch.empty_like(probs) if out is None else _check_out(out, probs)
     g = N.geometry(B, M, 0, w, M if other_rows is None else other_rows, other_off, seq)
     with torch.cuda.device(probs.device):
         N.check(N.lib.wmm_band_softmax_bwd(probs.data_ptr(), grad_probs.data_ptr(), grad_scores.data_ptr(), g,

@@ -45,6 +45,18 @@ def _mismatch(cond: bool) -> None:
         raise RuntimeError("Input mismatch")
 
 
+def _check_out(out: torch.Tensor, shape, like: torch.Tensor, band: bool) -> torch.Tensor:
+    """A caller-supplied output must be exactly what the kernel is about to write: the library sees only a pointer
+    (and, for the operand outputs, strides), so a wrong shape, dtype or device would be an out-of-bounds device write."""
+    _mismatch(isinstance(out, torch.Tensor) and tuple(out.shape) == tuple(shape))
+    _mismatch(out.dtype == like.dtype and out.device == like.device)
+    if band:        # band outputs are addressed as contiguous (B, M, 2w+1)
+        _mismatch(out.is_contiguous())
+    else:           # operand outputs go through their strides; elements must not overlap
+        _mismatch(all(st > 0 for st, n in zip(out.stride(), out.shape) if n > 1))
+    return out
+
+
 def _addressable(t: torch.Tensor) -> torch.Tensor:
     """A 3-D operand the kernels can address well: one of the two inner strides is 1."""
     if t.stride(-1) == 1 or t.stride(-2) == 1:
@@ -61,7 +73,8 @@ def band_nt(x, y, window, *, other_off=0, seq=None, out=None, flags=None):
     x, y = _addressable(x), _addressable(y)
     B, M, Nn = x.shape
     _mismatch(y.dim() == 3 and y.shape[0] == B and y.shape[2] == Nn)
-    band = torch.empty((B, M, 2 * window + 1), dtype=x.dtype, device=x.device) if out is None else out
+    shape = (B, M, 2 * window + 1)
+    band = torch.empty(shape, dtype=x.dtype, device=x.device) if out is None else _check_out(out, shape, x, True)
     g = N.geometry(B, M, Nn, window, y.shape[1], other_off, seq)
     with torch.cuda.device(x.device):
         N.check(N.lib.wmm_band_nt(N.operand(x), N.operand(y), band.data_ptr(), g, N.dtype_code(x),
@@ -76,7 +89,7 @@ def band_n(band, y, window, *, rows_out=None, other_off=0, seq=None, out=None, f
     B, M, W = band.shape
     _mismatch(W == 2 * window + 1 and y.dim() == 3 and y.shape[0] == B)
     Nn = y.shape[2]
-    o = torch.empty((B, M, Nn), dtype=y.dtype, device=y.device) if out is None else out
+    o = torch.empty((B, M, Nn), dtype=y.dtype, device=y.device) if out is None else _check_out(out, (B, M, Nn), y, False)
     g = N.geometry(B, M, Nn, window, y.shape[1], other_off, seq)
     with torch.cuda.device(y.device):
         N.check(N.lib.wmm_band_n(band.data_ptr(), N.operand(y), N.operand(o), g, N.dtype_code(y),
@@ -92,7 +105,7 @@ def band_t(band, x, window, *, other_rows=None, other_off=0, seq=None, out=None,
     _mismatch(W == 2 * window + 1 and x.dim() == 3 and x.shape[0] == B and x.shape[1] == M)
     Nn = x.shape[2]
     Mo = M if other_rows is None else other_rows
-    o = torch.empty((B, Mo, Nn), dtype=x.dtype, device=x.device) if out is None else out
+    o = torch.empty((B, Mo, Nn), dtype=x.dtype, device=x.device) if out is None else _check_out(out, (B, Mo, Nn), x, False)
     g = N.geometry(B, M, Nn, window, Mo, other_off, seq)
     with torch.cuda.device(x.device):
         N.check(N.lib.wmm_band_t(band.data_ptr(), N.operand(x), N.operand(o), g, N.dtype_code(x),
@@ -125,8 +138,8 @@ def window_matmul_backward(src, other, window_size, grad_output, need=(True, Tru
     src = _addressable(src)
     B, M, Nn = src.shape
     if need[0] and need[1]:
-        gq = torch.empty((B, M, Nn), dtype=src.dtype, device=src.device) if out is None else out[0]
-        gkt = torch.empty((B, M, Nn), dtype=src.dtype, device=src.device) if out is None else out[1]
+        gq = torch.empty((B, M, Nn), dtype=src.dtype, device=src.device) if out is None else _check_out(out[0], (B, M, Nn), src, False)
+        gkt = torch.empty((B, M, Nn), dtype=src.dtype, device=src.device) if out is None else _check_out(out[1], (B, M, Nn), src, False)
         g = N.geometry(B, M, Nn, window_size)
         with torch.cuda.device(src.device):
             N.check(N.lib.wmm_window_bwd(N.operand(src), N.operand(kt), grad_output.data_ptr(), N.operand(gq),
@@ -157,8 +170,9 @@ def unwindow_matmul_backward(src, other, window_size, grad_output, need=(True, T
     other, grad_output = _addressable(other), _addressable(grad_output)
     B, M, Nn = other.shape
     if need[0] and need[1]:
-        ga = torch.empty((B, M, 2 * window_size + 1), dtype=src.dtype, device=src.device) if out is None else out[0]
-        gv = torch.empty((B, M, Nn), dtype=src.dtype, device=src.device) if out is None else out[1]
+        ga = torch.empty((B, M, 2 * window_size + 1), dtype=src.dtype, device=src.device) if out is None \
+            else _check_out(out[0], (B, M, 2 * window_size + 1), src, True)
+        gv = torch.empty((B, M, Nn), dtype=src.dtype, device=src.device) if out is None else _check_out(out[1], (B, M, Nn), src, False)
         g = N.geometry(B, M, Nn, window_size)
         with torch.cuda.device(src.device):
             N.check(N.lib.wmm_unwindow_bwd(src.data_ptr(), N.operand(other), N.operand(grad_output), ga.data_ptr(),

@@ -28,7 +28,7 @@ def test_library_exports_every_declared_symbol():
     lib = ctypes.CDLL(N.LIB_PATH)
     for name in _declared():
         assert hasattr(lib, name), name
-    assert lib.wmm_version() == 1
+    assert lib.wmm_version() == 2
 
 
 def test_argument_validation_needs_no_gpu():
@@ -150,4 +150,36 @@ def test_halo_pull_argument_validation_needs_no_gpu():
     assert call([N.HaloBuffer(None, 512, 768)], both) == -1                # no local buffer
     before = N.launch_count()
     assert call([buf], both, batch=0) == 0                                 # empty: no launch
+    assert N.launch_count() == before
+
+
+def test_caller_supplied_outputs_are_validated_before_any_launch():
+    """The wrappers hand `out=` to the library as a bare pointer (plus strides for the operand outputs): shape, dtype,
+    device and layout are checked in Python first, with the reference's error wording (cuda/utils.cuh:3-4)."""
+    import importlib
+
+    import torch
+
+    from window_matmul import _native as N
+    from window_matmul import softmax as sm
+
+    impl = importlib.import_module("window_matmul.window_matmul")
+    like = torch.zeros(2, 8, 4)
+    before = N.launch_count()
+    assert impl._check_out(torch.empty(2, 8, 5), (2, 8, 5), like, True) is not None
+    bad_band = [torch.empty(2, 8, 7), torch.empty(2, 8, 5, dtype=torch.float64), torch.empty(2, 8, 10)[:, :, ::2],
+                torch.empty(2, 8, 5, device="meta"), None]
+    for out in bad_band:
+        with pytest.raises(RuntimeError, match="Input mismatch"):
+            impl._check_out(out, (2, 8, 5), like, True)
+    # operand outputs may be strided views, but not of another shape, nor with overlapping elements
+    assert impl._check_out(torch.empty(2, 8, 8)[:, :, :4], (2, 8, 4), like, False) is not None
+    for out in (torch.empty(2, 9, 4), torch.empty(8, 4).expand(2, 8, 4), torch.empty(2, 8, 4, dtype=torch.float16)):
+        with pytest.raises(RuntimeError, match="Input mismatch"):
+            impl._check_out(out, (2, 8, 4), like, False)
+    band = torch.zeros(2, 8, 5)
+    for out in (torch.empty(2, 8, 7), torch.empty(2, 8, 5, dtype=torch.float16), torch.empty(2, 8, 10)[:, :, ::2],
+                torch.empty(2 * 8 * 5 + 1)[1:].view(2, 8, 5)):
+        with pytest.raises(RuntimeError, match="Input mismatch"):
+            sm._check_out(out, band)
     assert N.launch_count() == before

@@ -170,8 +170,9 @@ def test_peer_memory_halo_exchange(tmp_path, dtype_name, shape):
 
 def test_halo_pull_wait_runs_out_without_hanging():
     """Failure detection of the exchange kernel on ONE GPU: the flag block of a 'neighbour' that never runs is plain local
-    memory that nothing sets.  The kernel's bounded waits (about a second each) run out, it returns, the status word has
-    bit 5 set, the margins are untouched and the context stays usable."""
+    memory that nothing sets.  The kernel's bounded waits (about a second for the neighbour to start, about three for its
+    acknowledgement) run out, it returns, the status word has bit 5 set, the margins are untouched and the context stays
+    usable."""
     import ctypes as C
 
     sys.path[:0] = [ROOT, os.path.join(ROOT, "pytorch-window-matmul_b200")]
@@ -183,7 +184,7 @@ def test_halo_pull_wait_runs_out_without_hanging():
     absent = torch.full((B, Ml + 2 * w, Nn), 7.0, dtype=torch.bfloat16, device=dev)   # stands in for the lower neighbour's buffer
     my_flags = torch.zeros(4, dtype=torch.int32, device=dev)
     absent_flags = torch.zeros(4, dtype=torch.int32, device=dev)                       # its ready word stays 0
-    counters = torch.zeros(2, dtype=torch.int32, device=dev)
+    counters = torch.zeros(4, dtype=torch.int32, device=dev)
     torch.cuda.synchronize()
     assert N.device_status() == 0
     bufs = (N.HaloBuffer * 1)(N.HaloBuffer(mine.data_ptr(), absent.data_ptr(), None))
@@ -195,7 +196,42 @@ def test_halo_pull_wait_runs_out_without_hanging():
     assert N.device_status() == 0                       # reading cleared it
     assert (mine == 1.0).all()                          # nothing was copied from a neighbour that was not ready
     assert int(my_flags[0]) == 1 and int(counters[0]) == 1 and int(counters[1]) == 0   # epoch advanced, CTA counter reset
+    assert int(absent_flags[2]) == 1                    # the acknowledgement went out although the copy was given up
     assert float((mine.float() + 1).sum()) > 0          # the context still works
+
+
+def test_halo_pull_serves_the_live_side_when_the_other_neighbour_is_absent():
+    """ONE GPU, two stand-in neighbours in local memory: the lower one never runs (its flag block stays zero), the upper
+    one looks as if it had started and finished (its ready word and its acknowledgement are written by the host before the
+    launch).  The kernel reports the lower side (bit 5), leaves the lower margin alone and still fills the upper margin
+    from the upper neighbour's first rows."""
+    import ctypes as C
+
+    sys.path[:0] = [ROOT, os.path.join(ROOT, "pytorch-window-matmul_b200")]
+    from window_matmul import _native as N
+
+    dev = torch.device("cuda", 0)
+    B, Ml, Nn, w = 3, 96, 64, 32      # several CTAs
+    ext = Ml + 2 * w
+    mine = torch.full((B, ext, Nn), 1.0, dtype=torch.bfloat16, device=dev)
+    lower = torch.full((B, ext, Nn), 7.0, dtype=torch.bfloat16, device=dev)
+    upper = torch.arange(B * ext * Nn, device=dev).remainder(251).to(torch.bfloat16).reshape(B, ext, Nn)
+    my_flags = torch.tensor([0, 0, 1, 0], dtype=torch.int32, device=dev)      # word 2: the upper neighbour's ack for epoch 1
+    lower_flags = torch.zeros(4, dtype=torch.int32, device=dev)
+    upper_flags = torch.tensor([1, 0, 0, 0], dtype=torch.int32, device=dev)   # ready for epoch 1
+    counters = torch.zeros(4, dtype=torch.int32, device=dev)
+    torch.cuda.synchronize()
+    assert N.device_status() == 0
+    bufs = (N.HaloBuffer * 1)(N.HaloBuffer(mine.data_ptr(), lower.data_ptr(), upper.data_ptr()))
+    flags = N.HaloFlags(my_flags.data_ptr(), lower_flags.data_ptr(), upper_flags.data_ptr(), counters.data_ptr())
+    stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    N.check(N.lib.wmm_halo_pull(bufs, 1, C.byref(flags), B, Ml, Nn, w, N.BF16, 0, stream))
+    torch.cuda.synchronize()
+    assert N.device_status() == 32
+    assert (mine[:, :w + Ml] == 1.0).all()                        # lower margin and own rows untouched
+    assert torch.equal(mine[:, w + Ml:], upper[:, w:2 * w])       # upper margin <- the upper neighbour's first own rows
+    assert int(upper_flags[1]) == 1 and int(lower_flags[2]) == 1  # both acknowledgements went out
+    assert int(counters[0]) == 1 and int(counters[1]) == 0
 
 
 def _peer_chain_worker(rank, world, port, shape, dtype_name, out_dir):
