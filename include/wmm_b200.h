@@ -219,6 +219,28 @@ typedef struct wmm_halo_flags {
 WMM_API int wmm_halo_pull(const wmm_halo_buffer *buffers, int count, const wmm_halo_flags *flags, int batch, int rows,
                           int cols, int window, int dtype, int accumulate, void *stream);
 
+/* wmm_halo_pull for callers that cannot allocate device memory.  No counterpart in the reference (it has no multi-GPU
+ * code).  Some users of this library run where cudaMalloc is not an option: an inference server that has handed all
+ * device memory to its own pool at start-up, a plugin called from a host callback or in the middle of a stream capture,
+ * where the runtime refuses allocations, or a real-time loop that must not take the allocator's lock.  wmm_halo_pull
+ * asks such a caller for four words of device memory (`counters`) that it has no good way to provide.  This entry
+ * point does the same exchange with those scratch words in a static device array inside the library instead:
+ * WMM_HALO_STATIC_LANES lanes of 256 bytes (2 KB in all), which every GPU that loads the library holds until the
+ * process exits.  It calls no allocation routine of any kind (no cudaMalloc / cudaFree, nothing of torch).
+ *   - `flags->counters` is not used (pass NULL).  The count of completed exchanges lives in word 3 of the caller's own
+ *     flag block `flags->mine` (which must therefore have its 4 words zeroed before the first call, like the rest of
+ *     the block), so a fresh flag block starts a fresh count whatever the lane was used for before.
+ *   - `lane` picks the scratch words: 0 <= lane < WMM_HALO_STATIC_LANES, anything else fails with WMM_ERR_TOO_LARGE.
+ *     All calls on a lane share its words; the call clears them (stream-ordered) before its kernel runs, so nothing of
+ *     an earlier call is carried over, but two calls on the SAME lane that overlap on the GPU (different streams,
+ *     no ordering between them) race.  Give sequence groups that may run at the same time different lanes.
+ *   - The first call on each device looks up the array's device address (with that device current).  Make that first
+ *     call outside of any stream capture.
+ * Everything else (buffers, flag hand-shake, waits, status bit 5) is as for wmm_halo_pull. */
+#define WMM_HALO_STATIC_LANES 8
+WMM_API int wmm_halo_pull_static(const wmm_halo_buffer *buffers, int count, const wmm_halo_flags *flags, int lane,
+                                 int batch, int rows, int cols, int window, int dtype, int accumulate, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -251,6 +251,40 @@ int wmm_halo_pull(const wmm_halo_buffer *buffers, int count, const wmm_halo_flag
   return WMM_OK;
 }
 
+// The neighbour exchange for callers that must not allocate: see include/wmm_b200.h.  Same checks as wmm_halo_pull, minus
+// the counters (the scratch words are the library's own), plus the lane.
+int wmm_halo_pull_static(const wmm_halo_buffer *buffers, int count, const wmm_halo_flags *flags, int lane, int batch,
+                         int rows, int cols, int window, int dtype, int accumulate, void *stream) {
+  if (!buffers || !flags) return fail(WMM_ERR_NULL, "halo buffers or flags are NULL");
+  if (lane < 0 || lane >= WMM_HALO_STATIC_LANES)
+    return fail(WMM_ERR_TOO_LARGE, "lane %d is outside the library's static scratch: it holds %d lanes (0 .. %d)", lane,
+                WMM_HALO_STATIC_LANES, WMM_HALO_STATIC_LANES - 1);
+  if (count < 1 || count > 4) return fail(WMM_ERR_SHAPE, "Input mismatch: 1 to 4 buffers per exchange, got %d", count);
+  const size_t e = elem_size(dtype);
+  if (e == 0) return fail(WMM_ERR_DTYPE, "unknown dtype code %d", dtype);
+  if (batch < 0 || rows < 0 || cols < 0 || window < 0)
+    return fail(WMM_ERR_SHAPE, "Input mismatch: negative extent (batch %d rows %d cols %d window %d)", batch, rows, cols, window);
+  if (rows < (accumulate ? 2 : 1) * (int64_t)window)
+    return fail(WMM_ERR_SHAPE, "Input mismatch: a shard of %d rows is too short for window %d", rows, window);
+  if ((int64_t)batch * cols * window == 0) return WMM_OK;
+  if (((int64_t)cols * e) % 16 != 0) return fail(WMM_ERR_STRIDE, "a row of %d elements is not a multiple of 16 bytes", cols);
+  if (!flags->mine) return fail(WMM_ERR_NULL, "flag block is NULL");
+  for (int i = 0; i < count; ++i) {
+    if (!buffers[i].local) return fail(WMM_ERR_NULL, "buffer %d has a NULL local pointer", i);
+    if (((uintptr_t)buffers[i].local | (uintptr_t)buffers[i].lower | (uintptr_t)buffers[i].upper) & 15)
+      return fail(WMM_ERR_STRIDE, "buffer %d is not 16-byte aligned", i);
+    if ((buffers[i].lower != nullptr) != (flags->lower != nullptr) || (buffers[i].upper != nullptr) != (flags->upper != nullptr))
+      return fail(WMM_ERR_NULL, "buffer %d and the flags disagree on which neighbours exist", i);
+  }
+  int launches = 0;
+  cudaError_t err = wmm::launch_halo_pull_static(buffers, count, *flags, lane, batch, rows, cols, window, dtype, accumulate != 0,
+                                                 (cudaStream_t)stream, &launches);
+  g_launches.fetch_add((uint64_t)launches, std::memory_order_relaxed);
+  if (err != cudaSuccess)
+    return fail(WMM_ERR_CUDA, "CUDA error in the halo exchange on static scratch (lane %d): %s", lane, cudaGetErrorString(err));
+  return WMM_OK;
+}
+
 uint64_t wmm_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int64_t wmm_device_status(int clear) {

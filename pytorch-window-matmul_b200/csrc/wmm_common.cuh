@@ -54,6 +54,12 @@ cudaError_t launch_halo_pull(const wmm_halo_buffer *bufs, int count, const wmm_h
                              unsigned *scratch, int batch, int rows, int cols, int window, int dtype, bool accumulate,
                              cudaStream_t stream, int *launches);
 
+// The same exchange with its scratch words in a static device array of the library (lane < WMM_HALO_STATIC_LANES) and
+// the exchange count in word 3 of flags.mine; no device memory is allocated.
+cudaError_t launch_halo_pull_static(const wmm_halo_buffer *bufs, int count, const wmm_halo_flags &flags, int lane, int batch,
+                                    int rows, int cols, int window, int dtype, bool accumulate, cudaStream_t stream,
+                                    int *launches);
+
 // Launchers describe a failure (which step, which driver code) here; the API layer appends it to the
 // error string of the calling thread.
 void set_launch_detail(const char *fmt, ...);

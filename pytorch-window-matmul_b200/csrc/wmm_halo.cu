@@ -24,6 +24,8 @@
 //       a rank whose OTHER neighbour is absent still acknowledges in time: only the ranks next to an absent one report
 //       a time-out.
 // Every wait is bounded by wall clock: a wait that runs out sets the status word (bit 5) and the kernel returns.
+#include <mutex>
+
 #include "wmm_common.cuh"
 
 namespace wmm {
@@ -234,6 +236,55 @@ cudaError_t launch_halo_pull(const wmm_halo_buffer *bufs, int count, const wmm_h
   cudaError_t err = cudaGetLastError();
   if (err == cudaSuccess && launches) ++*launches;
   return err;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// The exchange for callers that cannot allocate device memory (wmm_halo_pull_static).  The three scratch words of a
+// launch (CTAs done, go word per side) live in this array, which every device that loads the library holds until the
+// process ends: WMM_HALO_STATIC_LANES lanes of 256 bytes.  Calls on the same lane share their words; two such calls
+// that overlap on the GPU race.  The count of completed exchanges is NOT kept here but in word 3 of the caller's own
+// flag block, so it starts at zero with every new flag block, in step with the neighbours.
+// ---------------------------------------------------------------------------------------------------------------------
+namespace {
+constexpr int kLaneWords = 64;   // 256 bytes per lane
+static __device__ __align__(256) unsigned g_halo_static_scratch[WMM_HALO_STATIC_LANES * kLaneWords];
+
+// The device address of the array on the CURRENT device.  In host code the array's name is only a handle for the
+// runtime, not an address a kernel could use; the address is resolved once per device, with that device current.
+cudaError_t halo_static_base(unsigned **out) {
+  static std::mutex mu;
+  static unsigned *base[64] = {};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> lock(mu);
+  if (dev >= 0 && dev < 64 && base[dev]) {
+    *out = base[dev];
+    return cudaSuccess;
+  }
+  void *p = nullptr;
+  e = cudaGetSymbolAddress(&p, g_halo_static_scratch);
+  if (e != cudaSuccess) return e;
+  if (!p) return cudaErrorInvalidSymbol;
+  if (dev >= 0 && dev < 64) base[dev] = static_cast<unsigned *>(p);
+  *out = static_cast<unsigned *>(p);
+  return cudaSuccess;
+}
+}  // namespace
+
+cudaError_t launch_halo_pull_static(const wmm_halo_buffer *bufs, int count, const wmm_halo_flags &flags, int lane, int batch,
+                                    int rows, int cols, int window, int dtype, bool accumulate, cudaStream_t stream,
+                                    int *launches) {
+  unsigned *base = nullptr;
+  cudaError_t e = halo_static_base(&base);
+  if (e != cudaSuccess) return e;
+  unsigned *scratch = base + lane * kLaneWords;
+  // whatever the previous call on this lane left behind (another flag block's go words, a counter of a launch that was
+  // cut short) must not be read as this launch's: the lane starts from zero, in stream order
+  e = cudaMemsetAsync(scratch, 0, kLaneWords * sizeof(unsigned), stream);
+  if (e != cudaSuccess) return e;
+  return launch_halo_pull(bufs, count, flags, flags.mine + 3, scratch, batch, rows, cols, window, dtype, accumulate, stream,
+                          launches);
 }
 
 }  // namespace wmm

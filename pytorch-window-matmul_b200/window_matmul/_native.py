@@ -88,6 +88,8 @@ def _load():
     lib.wmm_unwindow_bwd.argtypes = [vp, P(Operand), P(Operand), vp, P(Operand), P(Geometry), i32, u32, vp]
     lib.wmm_halo_pull.restype = i32
     lib.wmm_halo_pull.argtypes = [P(HaloBuffer), i32, P(HaloFlags), i32, i32, i32, i32, i32, i32, vp]
+    lib.wmm_halo_pull_static.restype = i32
+    lib.wmm_halo_pull_static.argtypes = [P(HaloBuffer), i32, P(HaloFlags), i32, i32, i32, i32, i32, i32, i32, vp]
     lib.wmm_band_softmax.restype = i32
     lib.wmm_band_softmax.argtypes = [vp, vp, P(Geometry), i32, ctypes.c_float, u32, vp]
     lib.wmm_band_softmax_bwd.restype = i32
