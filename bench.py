@@ -39,8 +39,8 @@ WORKLOADS = {
     "c5": (64, 16384, 64, 384, "bf16", "normal"),
 }
 METRIC = "fwd+bwd window+unwindow us at B=96 M=4096 N=64 w=256"
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch, per band row, from the ncu capture summarised in
-# profiles/band_kernels_c2_b48_bf16.md (B=48: 196608 rows per launch).
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch, per band row, from an ncu capture of each kernel at
+# B=48 (196608 rows per launch).
 # (bytes per band row, bytes per launch).  The window backward (one sweep over grad_A) re-reads a fixed number of boxes at
 # the start of every CTA's run: 59.7 MB per launch whatever the batch, on top of 1461.8 B per band row.
 NCU_DRAM_BYTES_PER_ROW = {"c2": {"band_nt": (1008.8, 0.0), "band_n+band_t": (1461.8, 59.7e6), "band_n": (1245.0, 0.0),

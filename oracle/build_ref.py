@@ -59,7 +59,9 @@ def build(reference_root: str, with_cuda: bool = True, verbose: bool = False) ->
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    here = os.path.dirname(os.path.abspath(__file__))
+    ap.add_argument("--reference", default=os.environ.get("WMM_REFERENCE_ROOT", os.path.join(os.path.dirname(os.path.dirname(here)), "reference")),
+                    help="root of the reference's source tree (default: $WMM_REFERENCE_ROOT, else the directory `reference` beside this repository)")
     ap.add_argument("--cpu-only", action="store_true")
     ap.add_argument("-v", "--verbose", action="store_true")
     a = ap.parse_args()

@@ -4,7 +4,7 @@ import torch
 
 from oracle import oracle
 
-# Tolerances (north star of this build): exact-order fp32 within rtol 1e-5 / atol 1e-6 of the reference;
+# Tolerances: exact-order fp32 within rtol 1e-5 / atol 1e-6 of the reference;
 # 16-bit (fp32-accumulating tensor-core) results within 1e-2 relative of the fp32 reference on the
 # same (rounded) inputs.
 FP32_RTOL, FP32_ATOL = 1e-5, 1e-6
@@ -78,3 +78,51 @@ def out_of_sequence_mask(M, w):
     j = np.arange(2 * w + 1)[None, :]
     p = i + j - w
     return (p < 0) | (p >= M)
+
+
+# ---- oracle parity on row slices of sequences too long for the CPU ------------------------------------------------
+
+
+def slice_window(M, w, r0, r1):
+    """Rows [r0, r1) of all six results of the chain depend on positions [r0 - 2w, r1 + 2w) only (the band rows that
+    feed grad_K / grad_V of a position p are rows p-w .. p+w, and those rows see positions up to 2w away).  Returns
+    the truncated range [t0, t1) clipped to the sequence: the oracle run on it gives the exact values of those rows,
+    because for every band row within w of the slice the truncation cuts nothing the full sequence has."""
+    return max(0, r0 - 2 * w), min(M, r1 + 2 * w)
+
+
+def check_chain_slice(got, q, kt, v, go, w, b, r0, r1, rel=LOWP_REL, tag=""):
+    """Compares rows [r0, r1) of batch entry b of the GPU's a, o, ga, gv, gq, gk with the oracle.
+
+    `got`: GPU tensors a, ga (B,M,2w+1); o, gq, gv and gk (the gradient of K^T) (B,M,N).  q, kt, v, go: CPU tensors (B,M,N) holding the
+    (already rounded) values the GPU consumed.  Every contraction is checked on ITS OWN inputs as the GPU saw them: the
+    oracle of the second operator and of the backward passes is fed the GPU's rounded band tensors, so each result is
+    within `rel` of the reference arithmetic on identical inputs."""
+    M = q.shape[1]
+    t0, t1 = slice_window(M, w, r0, r1)
+    f = lambda t: np.ascontiguousarray(t[b:b + 1, t0:t1].float().cpu().numpy())  # noqa: E731
+    qs, kts, vs, gos = f(q), f(kt), f(v), f(go)
+    ks = np.ascontiguousarray(kts.transpose(0, 2, 1))
+    a_gpu, ga_gpu = f(got["a"]), f(got["ga"])
+    lo, hi = r0 - t0, r1 - t0
+    what = "%sb=%d rows [%d,%d)" % (tag, b, r0, r1)
+    a = oracle.window_matmul_forward(qs, ks, w)
+    assert_lowp_close(got["a"][b:b + 1, r0:r1], a[:, lo:hi], what + " a", rel)
+    o = oracle.unwindow_matmul_forward(a_gpu, vs, w)
+    assert_lowp_close(got["o"][b:b + 1, r0:r1], o[:, lo:hi], what + " o", rel)
+    ga, gv = oracle.unwindow_matmul_backward(a_gpu, vs, w, gos)
+    assert_lowp_close(got["ga"][b:b + 1, r0:r1], ga[:, lo:hi], what + " ga", rel)
+    assert_lowp_close(got["gv"][b:b + 1, r0:r1], gv[:, lo:hi], what + " gv", rel)
+    gq, gk = oracle.window_matmul_backward(qs, ks, w, ga_gpu)
+    assert_lowp_close(got["gq"][b:b + 1, r0:r1], gq[:, lo:hi], what + " gq", rel)
+    assert_lowp_close(got["gk"][b:b + 1, r0:r1], gk.transpose(0, 2, 1)[:, lo:hi], what + " gk", rel)
+
+
+def check_chain_slices(got, q, kt, v, go, w, cases, rel=LOWP_REL, tag=""):
+    """check_chain_slice over (b, r0, r1) cases, on host threads (the oracle releases the GIL inside its C loops)."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    with ThreadPoolExecutor(max_workers=8) as ex:
+        futs = [ex.submit(check_chain_slice, got, q, kt, v, go, w, b, r0, r1, rel, tag) for b, r0, r1 in cases]
+        for fu in futs:
+            fu.result()

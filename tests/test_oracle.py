@@ -126,3 +126,29 @@ def test_oracle_band_softmax_matches_the_torch_composition(M, w, mask):
     np.testing.assert_allclose(go, scores.grad.numpy(), rtol=1e-12, atol=1e-15)
     if mask:
         assert (po[:, outside.numpy()] == 0).all() and (go[:, outside.numpy()] == 0).all()
+
+
+def test_row_slices_of_a_truncated_sequence_equal_the_full_sequence():
+    """The slicing rule the full-size GPU tests rely on (helpers.slice_window / check_chain_slice): the oracle run on
+    positions [r0 - 2w, r1 + 2w) reproduces rows [r0, r1) of all six results of the chain on the whole sequence."""
+    import torch
+
+    import helpers as H
+
+    B, M, N, w = 2, 96, 8, 5
+    d = H.rand_inputs(B, M, N, w, seed=3)
+    q, kt, v, go = (torch.from_numpy(d[k]) for k in ("q", "kt", "v", "g_out"))
+    k = np.ascontiguousarray(d["kt"].transpose(0, 2, 1))
+    a, o, gq, gk, ga, gv = oracle.chain_fwd_bwd(d["q"], k, d["v"], w, d["g_out"])
+    got = {name: torch.from_numpy(np.ascontiguousarray(x)) for name, x in
+           dict(a=a, o=o, gq=gq, gk=gk.transpose(0, 2, 1), ga=ga, gv=gv).items()}
+    for b, r0, r1 in ((0, 0, 7), (1, 30, 41), (1, 80, 96), (0, 0, 96), (0, 9, 10)):
+        H.check_chain_slice(got, q, kt, v, go, w, b, r0, r1, rel=1e-6)
+    # and the check does notice a wrong row just inside a slice
+    bad = dict(got, gv=got["gv"].clone())
+    bad["gv"][1, 40] += 0.5
+    import pytest
+
+    with pytest.raises(AssertionError):
+        H.check_chain_slice(bad, q, kt, v, go, w, 1, 30, 41, rel=1e-6)
+    H.check_chain_slice(bad, q, kt, v, go, w, 1, 41, 52, rel=1e-6)   # ... and only there
