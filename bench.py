@@ -213,20 +213,20 @@ def run_reference(args, torch):
     print(json.dumps(line), flush=True)
 
 
-def run_reference_cuda(args, torch):
+def reference_cuda_summary(args, torch, steps=None):
     """The reference's own CUDA kernels (csrc/window_matmul/cuda/window_matmul_cuda.cu, compiled unmodified by
     oracle/build_ref.py) on this GPU, same workload, through its four pybind entry points.  The reference has
     no bf16: bf16 workloads run in fp16 (same bytes).  Reported beside our numbers, not part of the contract's
-    two arms."""
-    if int(os.environ.get("RANK", "0")) != 0:
-        return
+    two arms.  Returns a dict."""
     ref_dir = os.path.join(ROOT, "oracle", "_ref")
     if not os.path.exists(os.path.join(ref_dir, "WITH_CUDA")):
-        print(json.dumps({"impl": "reference_cuda", "unavailable": "oracle/_ref was built without the reference's CUDA sources"}))
-        return
+        return {"unavailable": "oracle/_ref was built without the reference's CUDA sources"}
     sys.path.insert(0, ref_dir)
-    import window_matmul_kernel as ref
-
+    try:
+        import window_matmul_kernel as ref
+    except Exception as ex:
+        return {"unavailable": "the compiled reference does not import: %s" % ex}
+    steps = steps or max(2, min(args.steps, 5))
     B, M, N, w, dt, dist = WORKLOADS[args.workload]
     dtype = {"bf16": torch.float16, "fp16": torch.float16, "fp32": torch.float32}[dt]
     e = 2 if dt != "fp32" else 4
@@ -239,22 +239,32 @@ def run_reference_cuda(args, torch):
         ga, _ = ref.unwindow_matmul_backward(a, v, w, go)
         ref.window_matmul_backward(q, k, w, ga)
 
-    for _ in range(max(1, args.warmup)):
+    for _ in range(2):
         step()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         step()
     e1.record()
     torch.cuda.synchronize()
-    us = e0.elapsed_time(e1) * 1e3 / args.steps
+    us = e0.elapsed_time(e1) * 1e3 / steps
     total_bytes, total_flops = algorithmic(B, M, N, w, e)
-    print(json.dumps({
-        "impl": "reference_cuda", "metric": "fwd+bwd window+unwindow us (%s)" % args.workload, "value": us, "unit": "us", "n_gpus": 1,
-        "steps": args.steps, "warmup": args.warmup, "dtype": "f16" if dt != "fp32" else "f32", "data": "synthetic",
-        "config": {"workload": workload_name(args.workload), "note": "reference CUDA kernels, legacy default stream, zero-filled outputs"},
-        "achieved_GBps": round(total_bytes / (us * 1e-6) / 1e9, 1), "TFLOPs": round(total_flops / (us * 1e-6) / 1e12, 2)}), flush=True)
+    return {"us": round(us, 1), "steps": steps, "dtype": "f16" if dt != "fp32" else "f32",
+            "note": "reference CUDA kernels (unmodified, sm_100), legacy default stream, zero-filled outputs, K as a transposed view",
+            "achieved_GBps": round(total_bytes / (us * 1e-6) / 1e9, 1), "TFLOPs": round(total_flops / (us * 1e-6) / 1e12, 2)}
+
+
+def run_reference_cuda(args, torch):
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    r = reference_cuda_summary(args, torch, steps=args.steps)
+    line = {"impl": "reference_cuda", "metric": "fwd+bwd window+unwindow us (%s)" % args.workload, "unit": "us", "n_gpus": 1,
+            "warmup": 2, "data": "synthetic", "config": {"workload": workload_name(args.workload)}}
+    line.update(r)
+    if "us" in r:
+        line["value"] = r["us"]
+    print(json.dumps(line), flush=True)
 
 
 def workload_name(key):
@@ -367,22 +377,40 @@ def run_ours(args, torch):
                 dist.barrier()
             torch.cuda.synchronize(dev)
 
-        # ---- device-resident timing: K steps between two events on the launching stream ----
-        launches0 = N_.launch_count()
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        with ClockSampler(local_rank) as clocks:
-            ev0.record(stream)
-            for _ in range(args.steps):
+        # ---- device-resident timing: blocks of exactly K steps, each between two events on the launching stream.
+        # `value` is the MEDIAN block (min and max are reported beside it): the blocks together span about a second, so
+        # the number is a sustained one and its spread is on record.
+        def run_steps(n):
+            for _ in range(n):
                 if graph is not None:
                     graph.replay()
                 else:
                     step()
-            ev1.record(stream)
+
+        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        p0.record(stream)
+        run_steps(3)
+        p1.record(stream)
+        stream.synchronize()
+        est_ms = max(1e-3, p0.elapsed_time(p1) / 3) * args.steps
+        blocks = args.blocks if args.blocks > 0 else int(min(400, max(50, math.ceil(1000.0 / est_ms))))
+        if dist_on:   # every rank times the same number of blocks
+            nb = torch.tensor([blocks], device=dev)
+            dist.all_reduce(nb, op=dist.ReduceOp.MAX)
+            blocks = int(nb[0])
+        launches0 = N_.launch_count()
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(blocks + 1)]
+        barrier()
+        with ClockSampler(local_rank) as clocks:
+            evs[0].record(stream)
+            for i in range(blocks):
+                run_steps(args.steps)
+                evs[i + 1].record(stream)
             stream.synchronize()
         barrier()
-        elapsed_ms = ev0.elapsed_time(ev1)
-        launches = (N_.launch_count() - launches0) if graph is None else args.steps * launches_per_step
+        block_ms = sorted(evs[i].elapsed_time(evs[i + 1]) for i in range(blocks))
+        elapsed_ms, block_min_ms, block_max_ms = block_ms[len(block_ms) // 2], block_ms[0], block_ms[-1]
+        launches = (N_.launch_count() - launches0) if graph is None else blocks * args.steps * launches_per_step
 
         # ---- per-kernel durations (for the roofline of the dominant kernel) ----
         per_kernel = {}
@@ -490,21 +518,26 @@ def run_ours(args, torch):
         e2e_steps = max(3, min(args.steps, 20))
         outs_host = [torch.empty(Bl, M, N, dtype=dtype).pin_memory() for _ in range(4)]
 
-        from window_matmul.host_pipeline import batched_host_call
+        from window_matmul.host_pipeline import HostPipeline
+
+        pipe = HostPipeline(dev)
 
         def chain(qh, kth, vh, goh):
-            """The four native calls of the reference's module (window_matmul_kernel.*: forward and backward of
-            both operators) on one device-resident chunk of the batch; results are freshly allocated."""
-            kh = kth.transpose(-1, -2)
-            att = impl.window_matmul_forward(qh, kh, w)
-            out = impl.unwindow_matmul_forward(att, vh, w)
-            g_att, g_v = impl.unwindow_matmul_backward(att, vh, w, goh)
-            g_q, g_k = impl.window_matmul_backward(qh, kh, w, g_att)
-            return out, g_q, g_k.transpose(-1, -2), g_v
+            """What a user of the package writes: the two differentiable operators and .backward() on one device-resident
+            chunk of the batch.  Returns the output and the three gradients."""
+            qd_, ktd_, vd_ = (t.detach().requires_grad_(True) for t in (qh, kth, vh))
+            att = pkg.window_matmul(qd_, ktd_.transpose(-1, -2), w)
+            out = pkg.unwindow_matmul(att, vd_, w)
+            out.backward(goh)
+            return out.detach(), qd_.grad, ktd_.grad, vd_.grad
+
+        # a handful of chunks: enough for uploads, kernels and downloads to overlap, few enough that the host-side cost
+        # per chunk (autograd, ~10 launches) stays small against the copies
+        e2e_chunks = args.e2e_chunks if args.e2e_chunks > 0 else max(3, min(8, Bl // 12))
 
         def e2e_step():
             # host tensors in, host tensors out; uploads, kernels and downloads of batch chunks overlap
-            batched_host_call(chain, host, chunks=args.e2e_chunks, device=dev, outputs=outs_host)
+            pipe(chain, host, chunks=e2e_chunks, outputs=outs_host)
 
         run_e2e = Bl > 0 and not args.skip_e2e
         if run_e2e:
@@ -526,10 +559,10 @@ def run_ours(args, torch):
         raise SystemExit("bench.py: a kernel abandoned a bounded wait (device status %d); numbers are void" % status)
 
     # max over ranks, on the device clock
-    t = torch.tensor([elapsed_ms, e2e_ms], dtype=torch.float64, device=dev)
+    t = torch.tensor([elapsed_ms, e2e_ms, block_min_ms, block_max_ms], dtype=torch.float64, device=dev)
     if dist_on:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    elapsed_ms, e2e_ms = float(t[0]), float(t[1])
+    elapsed_ms, e2e_ms, block_min_ms, block_max_ms = (float(x) for x in t)
     us_per_step = elapsed_ms * 1e3 / args.steps
 
     if rank == 0:
@@ -544,6 +577,10 @@ def run_ours(args, torch):
         line = {
             "metric": METRIC if args.workload == "c2" and not args.batch else "fwd+bwd window+unwindow us (%s)" % args.workload,
             "value": us_per_step, "unit": "us", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+            "blocks": {"n": blocks, "steps_each": args.steps, "value_is": "median block, max over ranks",
+                       "min_us": round(block_min_ms * 1e3 / args.steps, 2), "median_us": round(us_per_step, 2),
+                       "max_us": round(block_max_ms * 1e3 / args.steps, 2),
+                       "timed_s": round(sum(block_ms) / 1e3, 3)},
             "ms_per_step": us_per_step / 1e3, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
             "dtype": dt.replace("fp", "f"), "data": "synthetic",
             "config": {
@@ -567,7 +604,8 @@ def run_ours(args, torch):
             "attention_block": block,
             "e2e": {
                 "value": e2e_ms * 1e3 if run_e2e else None, "unit": "us", "h2d_bytes_per_step": 4 * Bl * M * N * e * world,
-                "d2h_bytes_per_step": 4 * Bl * M * N * e * world, "steps": e2e_steps,
+                "d2h_bytes_per_step": 4 * Bl * M * N * e * world, "steps": e2e_steps, "chunks_per_gpu": e2e_chunks,
+                "api": "window_matmul.window_matmul -> window_matmul.unwindow_matmul -> .backward() per batch chunk, pinned host buffers",
             },
             "gpu_launches": int(launches),
             "clocks": clocks.summary(),
@@ -587,33 +625,82 @@ def run_ours(args, torch):
                 "sample": "B=%d M=%d of B=%d M=%d, fp32 on %s-rounded inputs, %.2f s measured, x%.1f extrapolated; host has %d cores, "
                           "the reference's loops use one" % (Bs, Ms, B, M, dt, secs, scale, os.cpu_count()),
             }
+        if world == 1 and not args.no_reference_cuda and not args.batch:
+            line["reference_cuda"] = reference_cuda_summary(args, torch)
+    if dist_on and args.workload == "c2" and not args.no_seq_extra and not args.batch:
+        # the other multi-GPU partitioning, on the same ranks: config 4 split along the sequence with halo exchange
+        try:
+            seq = measure_seq_sharded(args, torch, impl, N_, rank, world, dev, "c4", max(5, min(args.steps, 20)))
+        except Exception as ex:   # reported, never hides the headline
+            seq = {"error": "%s: %s" % (type(ex).__name__, ex)}
+        if rank == 0:
+            line["seq_sharded"] = seq
+    if rank == 0:
         print(json.dumps(line), flush=True)
     if dist_on:
         dist.destroy_process_group()
 
 
-def run_seq_sharded(args, torch, impl, N_, rank, world, dev):
-    """Sequence-sharded step (config 4): rank r owns rows [r*M/P, (r+1)*M/P) of every tensor; K^T and V rows
-    within w of a shard edge are exchanged with the neighbours before the forward contractions, partial
-    grad_K / grad_V rows after the backward ones (window_matmul/sharded.py).  Same six contractions, same
-    job at every P (strong scaling); time = max over ranks on device clocks."""
+def _seq_rank_inputs(torch, r, B, Ml, N, distn, dtype):
+    """The rows rank r owns, from a CPU generator seeded by r: any rank can regenerate a neighbour's rows."""
+    g = torch.Generator(device="cpu").manual_seed(1000 + r)
+    s = 1.0 / N ** 0.5 if distn == "normal_scaled" else 1.0
+    q, kt, v = ((torch.randn(B, Ml, N, generator=g) * s).to(dtype) for _ in range(3))
+    go = torch.randn(B, Ml, N, generator=g).to(dtype)
+    return q, kt, v, go
+
+
+def _seq_parity(torch, impl, dev, workload, world, got, mine):
+    """Rank 0's rows of all six results against the UNSHARDED kernels of this library on the same seeded rows: rows
+    [0, Ml) of a sequence depend on positions below Ml + 2w only, so the plain operators run on rank 0's rows plus the
+    first 2w rows of rank 1 (regenerated from rank 1's seed).  Returns, per tensor, max |x - y| / (1e-2 (|y| + rms(y)));
+    <= 1 means within the 16-bit bound.  The sharded grad_K / grad_V edge rows are sums of two rounded partial rows, so
+    they differ from the unsharded rows by a rounding, not bit for bit."""
+    B, M, N, w, dt, distn = WORKLOADS[workload]
+    dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[dt]
+    Ml = M // world
+    q, kt, v, go = mine
+    if world > 1:
+        nq, nkt, nv, ngo = _seq_rank_inputs(torch, 1, B, Ml, N, distn, dtype)
+        q, kt, v, go = (torch.cat([x, y[:, :2 * w]], dim=1) for x, y in ((q, nq), (kt, nkt), (v, nv), (go, ngo)))
+    q, kt, v, go = (t.to(dev) for t in (q, kt, v, go))
+    ra = impl.band_nt(q, kt, w)
+    ro = impl.band_n(ra, v, w)
+    rga = impl.band_nt(go, v, w)
+    rgv = impl.band_t(ra, go, w)
+    rgq = impl.band_n(rga, kt, w)
+    rgk = impl.band_t(rga, q, w)
+    out = {}
+    for name, x, y in (("a", got["a"], ra), ("o", got["o"], ro), ("ga", got["ga"], rga), ("gq", got["gq"], rgq),
+                       ("gk", got["gk"], rgk), ("gv", got["gv"], rgv)):
+        y = y[:, :Ml].float()
+        x = x.float()
+        rms = float(y.pow(2).mean().sqrt())
+        out[name] = round(float(((x - y).abs() / (1e-2 * (y.abs() + rms) + 1e-30)).max()), 4)
+    out["max_err_over_bound"] = max(out.values())
+    return out
+
+
+def measure_seq_sharded(args, torch, impl, N_, rank, world, dev, workload, steps, parity=True):
+    """Sequence-sharded step (config 4): rank r owns rows [r*M/P, (r+1)*M/P) of every tensor; K^T and V rows within w
+    of a shard edge are exchanged with the neighbours before the forward contractions, partial grad_K / grad_V rows
+    after the backward ones.  Same six contractions, same job at every P (strong scaling); time = max over ranks on
+    device clocks.  Returns a dict (the same on every rank).  Needs an initialised process group when world > 1."""
     import torch.distributed as dist
 
     from window_matmul import sharded
 
-    B, M, N, w, dt, distn = WORKLOADS[args.workload]
+    B, M, N, w, dt, distn = WORKLOADS[workload]
     dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[dt]
     e = 2 if dt != "fp32" else 4
     Ml = M // world
-    g = torch.Generator(device="cpu").manual_seed(rank)
-    s = 1.0 / N ** 0.5 if distn == "normal_scaled" else 1.0
-    q = (torch.randn(B, Ml, N, generator=g) * s).to(dtype).to(dev)
+    qc, ktc, vc, goc = _seq_rank_inputs(torch, rank, B, Ml, N, distn, dtype)
+    q, go = qc.to(dev), goc.to(dev)
     # K^T and V live in storage with halo margins, so the exchange writes only the margins
     kt, _ = sharded.alloc_with_halo(B, Ml, N, w, dtype, dev)
     v, _ = sharded.alloc_with_halo(B, Ml, N, w, dtype, dev)
-    kt.copy_((torch.randn(B, Ml, N, generator=g) * s).to(dtype))
-    v.copy_((torch.randn(B, Ml, N, generator=g) * s).to(dtype))
-    go = torch.randn(B, Ml, N, generator=g).to(dtype).to(dev)
+    kt.copy_(ktc)
+    v.copy_(vc)
     W = 2 * w + 1
     a = torch.empty(B, Ml, W, dtype=dtype, device=dev)
     ga = torch.empty_like(a)
@@ -630,10 +717,9 @@ def run_seq_sharded(args, torch, impl, N_, rank, world, dev):
     #     memory (window_matmul/peer_halo.py); the whole step, exchanges included, replays as one CUDA graph.
     #   --exchange nccl: torch.distributed send/recv pairs (window_matmul/sharded.py) around a graph of the six
     #     contractions; each exchange costs ~120 us of host time per rank, which binds the step at 8 ranks.
-    # Overlapping the exchanges with the contractions on a second stream measured slower (persistent kernels: a concurrent
-    # kernel waits for an SM until they finish), so they run in stream order.
     peer = world > 1 and args.exchange == "peer"
     parts = {}
+    ph = None
     if peer:
         from window_matmul.peer_halo import PeerHalo
 
@@ -641,13 +727,20 @@ def run_seq_sharded(args, torch, impl, N_, rank, world, dev):
         ph.local(0).copy_(kt)
         ph.local(1).copy_(v)
 
+    launch_list = [
+        ("window_fwd band_nt", lambda k_, v_: impl.band_nt(q, k_, w, other_off=off, seq=seq, out=a)),
+        ("unwindow_fwd band_n", lambda k_, v_: impl.band_n(a, v_, w, other_off=off, seq=seq, out=o)),
+        ("unwindow_bwd grad_A band_nt", lambda k_, v_: impl.band_nt(go, v_, w, other_off=off, seq=seq, out=ga)),
+        ("unwindow_bwd grad_V band_t", lambda k_, v_: parts.__setitem__("gv", impl.band_t(
+            a, go, w, other_rows=ext, other_off=off, seq=seq, out=ph.partial(1) if peer else None))),
+        ("window_bwd grad_Q band_n", lambda k_, v_: impl.band_n(ga, k_, w, other_off=off, seq=seq, out=gq)),
+        ("window_bwd grad_K band_t", lambda k_, v_: parts.__setitem__("gk", impl.band_t(
+            ga, q, w, other_rows=ext, other_off=off, seq=seq, out=ph.partial(0) if peer else None))),
+    ]
+
     def contractions(kt_ext, v_ext):
-        impl.band_nt(q, kt_ext, w, other_off=off, seq=seq, out=a)
-        impl.band_n(a, v_ext, w, other_off=off, seq=seq, out=o)
-        impl.band_nt(go, v_ext, w, other_off=off, seq=seq, out=ga)
-        parts["gv"] = impl.band_t(a, go, w, other_rows=ext, other_off=off, seq=seq, out=ph.partial(1) if peer else None)
-        impl.band_n(ga, kt_ext, w, other_off=off, seq=seq, out=gq)
-        parts["gk"] = impl.band_t(ga, q, w, other_rows=ext, other_off=off, seq=seq, out=ph.partial(0) if peer else None)
+        for _, fn in launch_list:
+            fn(kt_ext, v_ext)
 
     def barrier():
         torch.cuda.synchronize(dev)
@@ -657,6 +750,7 @@ def run_seq_sharded(args, torch, impl, N_, rank, world, dev):
 
     stream = torch.cuda.Stream(device=dev)
     graph = None
+    result = {}
     with torch.cuda.stream(stream):
         def raw_step():
             if peer:
@@ -673,16 +767,22 @@ def run_seq_sharded(args, torch, impl, N_, rank, world, dev):
         def step():
             if peer and graph is not None:
                 graph.replay()
-            else:
-                raw_step()
+                return None
+            return raw_step()
 
         for _ in range(max(3, args.warmup)):
             step()
         stream.synchronize()
         l0 = N_.launch_count()
-        step()
+        grads = step()
         launches_per_step = N_.launch_count() - l0
         stream.synchronize()
+
+        # ---- parity, outside the timed region: rank 0's rows against the unsharded kernels on the same seeded rows ----
+        if parity and rank == 0:
+            gk_l, gv_l = (grads[0], grads[1]) if peer else (grads[1], grads[0])
+            result["parity"] = _seq_parity(torch, impl, dev, workload, world, dict(a=a, o=o, ga=ga, gq=gq, gk=gk_l, gv=gv_l),
+                                           (qc, ktc, vc, goc))
         if not args.no_graph:
             g_ = torch.cuda.CUDAGraph()
             if peer:
@@ -702,39 +802,88 @@ def run_seq_sharded(args, torch, impl, N_, rank, world, dev):
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with ClockSampler(dev.index) as clocks:
             ev0.record(stream)
-            for _ in range(args.steps):
+            for _ in range(steps):
                 step()
             ev1.record(stream)
             stream.synchronize()
         barrier()
-    launches = launches_per_step * args.steps
-    if N_.device_status() != 0:
-        raise SystemExit("bench.py: a kernel abandoned a bounded wait; numbers are void")
-    t = torch.tensor([ev0.elapsed_time(ev1)], dtype=torch.float64, device=dev)
+
+        # ---- per-launch durations: every rank issues the same launch, `reps` times, between two barriers ----
+        per_launch = []
+        reps = 5
+        if peer:
+            kt_ext, v_ext = ph.exchange()
+            seq_launches = ([("halo_pull K^T+V margins", lambda k_, v_: ph.exchange())] + launch_list +
+                            [("halo_pull grad_K+grad_V reduction", lambda k_, v_: ph.reduce())])
+        else:
+            kt_ext, v_ext = halo([kt, v])
+            seq_launches = launch_list
+        for name, fn in seq_launches:
+            fn(kt_ext, v_ext)
+            barrier()
+            k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            k0.record(stream)
+            for _ in range(reps):
+                fn(kt_ext, v_ext)
+            k1.record(stream)
+            stream.synchronize()
+            per_launch.append(k0.elapsed_time(k1) * 1e3 / reps)
+        barrier()
+    status = N_.device_status()
+    t = torch.tensor([ev0.elapsed_time(ev1), float(status)] + per_launch, dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    us = float(t[0]) * 1e3 / args.steps
+    us = float(t[0]) * 1e3 / steps
+    total_bytes, total_flops = algorithmic(B, M, N, w, e)
+    peak, peak_kind = measured_peaks()
+    result.update({
+        "value_us": us, "n_gpus": world, "steps": steps, "workload": workload_name(workload), "rows_per_gpu": Ml,
+        "exchange": ("peer memory: one kernel of the library per exchange" if peer else
+                     "NCCL send/recv (torch.distributed)" if world > 1 else "none"),
+        "halo_bytes_per_rank_step": 0 if world == 1 else 4 * 2 * B * w * N * e,  # K^T, V margins in; grad_K, grad_V partials in
+        "launch": ("stream launches" if graph is None else "one cuda graph per step (exchanges and contractions)" if peer
+                   else "cuda graph of the six contractions between two NCCL exchanges"),
+        "launches_per_step": int(launches_per_step),
+        "per_launch_us_max_over_ranks": {name: round(float(x), 1) for (name, _), x in zip(seq_launches, t[2:].tolist())},
+        "alg_MB": round(total_bytes / 1e6, 1),
+        "frac_of_%s_hbm" % peak_kind: round(total_bytes / world / (us * 1e-6) / 1e9 / peak, 4),
+        "device_status": int(t[1]), "clocks": clocks.summary(),
+    })
+    if world > 1:   # every rank returns the same dict (rank 0 holds the parity figures)
+        box = [result if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        result = box[0]
+    del ph
+    return result
+
+def run_seq_sharded(args, torch, impl, N_, rank, world, dev):
+    """bench.py --shard seq (the default for --workload c4 on several GPUs): prints the sequence-sharded step as its own line."""
+    r = measure_seq_sharded(args, torch, impl, N_, rank, world, dev, args.workload, args.steps)
+    if r["device_status"] != 0:
+        raise SystemExit("bench.py: a kernel abandoned a bounded wait; numbers are void")
     if rank == 0:
-        peak, peak_kind = measured_peaks()
+        B, M, N, w, dt, distn = WORKLOADS[args.workload]
+        e = 2 if dt != "fp32" else 4
         total_bytes, total_flops = algorithmic(B, M, N, w, e)
-        halo_bytes = 0 if world == 1 else 4 * 2 * B * w * N * e  # per interior rank and step: K^T, V out and grad halos back
+        us = r["value_us"]
         line = {
             "metric": "fwd+bwd window+unwindow us (%s, sequence-sharded)" % args.workload, "value": us, "unit": "us", "n_gpus": world,
             "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": us / 1e3, "higher_is_better": False,
             "scaling": "strong", "vs_baseline": None, "dtype": dt.replace("fp", "f"), "data": "synthetic",
-            "config": {"workload": workload_name(args.workload), "parallelism": "sequence-sharded x%d, w-row halo exchange" % world,
-                       "rows_per_gpu": Ml, "halo_bytes_per_rank_step": halo_bytes,
-                       "exchange": ("peer memory: one kernel of the library per exchange" if peer else "NCCL send/recv (torch.distributed)"),
-                       "launch": ("stream launches" if graph is None else "one cuda graph per step (exchanges and contractions)" if peer
-                                  else "cuda graph of the six contractions between two NCCL exchanges"),
+            "config": {"workload": r["workload"], "parallelism": "sequence-sharded x%d, w-row halo exchange" % world,
+                       "rows_per_gpu": r["rows_per_gpu"], "halo_bytes_per_rank_step": r["halo_bytes_per_rank_step"],
+                       "exchange": r["exchange"], "launch": r["launch"],
                        "l2": "no flush: one step touches %.0f MB per GPU" % (total_bytes / world / 1e6)},
-            "step_roofline": {"alg_MB": round(total_bytes / 1e6, 1), "alg_GFLOP": round(total_flops / 1e9, 1),
+            "step_roofline": {"alg_MB": r["alg_MB"], "alg_GFLOP": round(total_flops / 1e9, 1),
                               "achieved_GBps": round(total_bytes / (us * 1e-6) / 1e9, 1),
-                              "frac_of_%s_hbm" % peak_kind: round(total_bytes / world / (us * 1e-6) / 1e9 / peak, 4)},
-            "gpu_launches": int(launches), "clocks": clocks.summary(),
+                              **{k: v for k, v in r.items() if k.startswith("frac_of_")}},
+            "per_launch_us_max_over_ranks": r["per_launch_us_max_over_ranks"], "parity_vs_unsharded": r.get("parity"),
+            "gpu_launches": int(r["launches_per_step"] * args.steps), "clocks": r["clocks"],
         }
         print(json.dumps(line), flush=True)
     if world > 1:
+        import torch.distributed as dist
+
         dist.destroy_process_group()
 
 
@@ -745,6 +894,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference_cuda"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--blocks", type=int, default=0, help="timed blocks of --steps steps each (0: enough for about a second, at least 50)")
+    ap.add_argument("--no-reference-cuda", action="store_true", help="skip the short run of the reference's CUDA kernels beside the headline")
+    ap.add_argument("--no-seq-extra", action="store_true", help="on several GPUs: skip the sequence-sharded config 4 step reported beside the headline")
     ap.add_argument("--branches", type=int, default=2, choices=[1, 2], help="capture the step as one chain (1) or with its real dependencies (2)")
     ap.add_argument("--no-graph", action="store_true", help="launch the six kernels on the stream instead of a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -753,7 +905,7 @@ def main():
                     help="K as a transposed view of a (B,M,N) tensor (default) or as a contiguous (B,N,M) tensor")
     ap.add_argument("--shard", default="auto", choices=["auto", "batch", "seq"],
                     help="multi-GPU partitioning: batch entries (default) or sequence rows with halo exchange (default for c4)")
-    ap.add_argument("--e2e-chunks", type=int, default=8, help="batch chunks of the host-buffer leg")
+    ap.add_argument("--e2e-chunks", type=int, default=0, help="batch chunks of the host-buffer leg (0: from the batch per GPU)")
     ap.add_argument("--skip-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="sequence-sharded mode: halo exchange through peer memory (one library kernel) or NCCL send/recv")

@@ -36,15 +36,21 @@ def _stale(target, sources):
     return any(os.path.getmtime(s) > t for s in sources)
 
 
-def build(force=False, verbose=False):
-    os.makedirs(OBJ, exist_ok=True)
+def build(force=False, verbose=False, defines=(), out=None):
+    """`defines` (e.g. ["WMM_TRACE"]) build a variant of the library: objects go to their own directory and `out` names
+    the shared object, so the normal library is left alone."""
+    obj_dir = OBJ + ("_" + "_".join(defines) if defines else "")
+    lib = out or LIB
+    if defines and out is None:
+        raise ValueError("a variant build needs its own output path")
+    os.makedirs(obj_dir, exist_ok=True)
     deps = _deps()
     jobs = []
     for src in SOURCES:
         s = os.path.join(CSRC, src)
-        o = os.path.join(OBJ, src[:-3] + ".o")
+        o = os.path.join(obj_dir, src[:-3] + ".o")
         if force or _stale(o, [s] + deps):
-            cmd = [NVCC] + FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
+            cmd = [NVCC] + FLAGS + ["-D" + d for d in defines] + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
             jobs.append(cmd)
 
     def run(cmd):
@@ -56,16 +62,18 @@ def build(force=False, verbose=False):
 
     with ThreadPoolExecutor(max_workers=4) as ex:
         list(ex.map(run, jobs))
-    objs = [os.path.join(OBJ, s[:-3] + ".o") for s in SOURCES]
-    if force or jobs or _stale(LIB, objs):
-        cmd = [NVCC, "-shared", "-o", LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a"]
+    objs = [os.path.join(obj_dir, s[:-3] + ".o") for s in SOURCES]
+    if force or jobs or _stale(lib, objs):
+        cmd = [NVCC, "-shared", "-o", lib] + objs + ["-gencode", "arch=compute_100a,code=sm_100a"]
         run(cmd)
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("-v", "--verbose", action="store_true")
+    ap.add_argument("-D", "--define", action="append", default=[], help="preprocessor define for a variant build (with --out)")
+    ap.add_argument("--out", default=None, help="path of the shared object of a variant build")
     a = ap.parse_args()
-    print(build(a.force, a.verbose))
+    print(build(a.force, a.verbose, tuple(a.define), a.out))

@@ -51,6 +51,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   const uint64_t t0 = globaltimer_ns();
   for (uint32_t spin = 1;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
+#ifdef WMM_SPIN_SLEEP
+    __nanosleep(WMM_SPIN_SLEEP);
+#endif
     if ((spin & 63u) == 0u) {
       if (*abort_flag) return false;
       if (globaltimer_ns() - t0 > kWaitLimitNs) {
@@ -70,6 +73,14 @@ __device__ __forceinline__ void tc_fence_after_sync() { asm volatile("tcgen05.fe
 __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
+
+// ---- programmatic dependent launch ----------------------------------------------------------------
+// A kernel launched with the programmatic-stream-serialization attribute may start while its predecessor in the stream
+// still runs.  launch_dependents: this CTA no longer minds the next kernel of the stream being scheduled (it gets SMs
+// only as CTAs of this kernel exit).  wait: returns once the predecessor has completed and its memory is visible; nothing
+// before it may touch global memory that the predecessor reads or writes.  Both are no-ops in a plain launch.
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // ---- TMA ------------------------------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap *m) {

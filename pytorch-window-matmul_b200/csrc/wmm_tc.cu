@@ -15,7 +15,9 @@
 // TMEM owner, warps 2-5 = epilogue (TMEM -> registers -> global / staging + TMA store).
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
+#include <utility>
 
 #include "wmm_common.cuh"
 #include "wmm_ptx.cuh"
@@ -39,6 +41,39 @@ unsigned long long *device_status_word() {
   return cudaGetSymbolAddress(&p, g_device_status) == cudaSuccess ? static_cast<unsigned long long *>(p) : nullptr;
 }
 
+// Per-CTA timeline for tuning (build with -DWMM_TRACE): kernels store the global timer at a few points of their life;
+// wmm_trace_read() copies the table out.  Compiled out of the normal library.
+#ifdef WMM_TRACE
+constexpr int kTraceSlots = 160;
+__device__ unsigned long long g_trace[160 * kTraceSlots];
+#define WMM_TRACE_POINT(id)                                                                     \
+  do {                                                                                          \
+    if (blockIdx.x < 160) g_trace[blockIdx.x * kTraceSlots + (id)] = ptx::globaltimer_ns();     \
+  } while (0)
+// time accumulated in a REGISTER by the caller (no memory traffic inside the loops), stored once with WMM_TRACE_STORE
+#define WMM_TRACE_T0(var) const unsigned long long var = ptx::globaltimer_ns()
+#define WMM_TRACE_ACC(acc, var) acc += ptx::globaltimer_ns() - var
+#define WMM_TRACE_STORE(id, value)                                                  \
+  do {                                                                              \
+    if (blockIdx.x < 160) g_trace[blockIdx.x * kTraceSlots + (id)] = (value);       \
+  } while (0)
+extern "C" __attribute__((visibility("default"))) int wmm_trace_read(unsigned long long *out, int clear) {
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace));
+  if (e == cudaSuccess && clear) {
+    void *p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_trace);
+    if (e == cudaSuccess) e = cudaMemset(p, 0, sizeof(g_trace));
+  }
+  return e == cudaSuccess ? 160 * kTraceSlots : -1;
+}
+#else
+#define WMM_TRACE_POINT(id) ((void)0)
+#define WMM_TRACE_T0(var) ((void)0)
+#define WMM_TRACE_ACC(acc, var) ((void)0)
+#define WMM_TRACE_STORE(id, value) ((void)0)
+#endif
+
 namespace {
 thread_local char tls_detail[256] = "";
 }
@@ -56,7 +91,7 @@ using namespace ptx;
 
 constexpr int TILE = 128;       // band rows per tile = MMA M
 constexpr int CHUNK = 128;      // positions per chunk = MMA N of band_nt
-constexpr int ACC_STAGES = 8;   // band_nt: 8 x 64 TMEM columns
+constexpr int ACC_STAGES = 4;   // band_nt: 4 x 128 TMEM columns (one chunk each)
 // Status codes OR-ed into g_device_status when a bounded wait runs out: bit 0 band_nt, bit 1 band_n / band_t.
 
 // A (128 rows x NH) 16-bit operand tile in shared memory, K-major, written by TMA with the hardware
@@ -143,6 +178,24 @@ int persistent_grid(int items) {
   return items < sms ? items : sms;
 }
 
+// Launch with programmatic stream serialization: the kernel may be scheduled while its predecessor in the stream is
+// still running; its prologue then overlaps the predecessor's tail and it blocks at griddepcontrol.wait (see wmm_ptx.cuh)
+// before touching global memory.  Captured into CUDA graphs as a programmatic dependency edge.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kern)(KArgs...), int grid, int block, size_t smem, cudaStream_t stream, Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3((unsigned)block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
+}
+
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 CUtensorMapSwizzle swizzle_for(int bytes) {
@@ -216,7 +269,7 @@ bool y_position_major(const Problem &p) {
 
 bool band_tma_ok(const void *band, int M, int w) { return aligned16(band) && (w % 4) == 0 && w >= 4 && (M % 8) == 0; }
 
-template <bool BF16, int NH, bool YMN> cudaError_t launch_nt(const Problem &p, cudaStream_t stream) {
+template <bool BF16, int NH, bool YMN, bool PAIRED> cudaError_t launch_nt(const Problem &p, cudaStream_t stream) {
   using S = NtSmem<NH>;
   using OT = KMajorTile<NH>;
   NtParams k;
@@ -224,9 +277,13 @@ template <bool BF16, int NH, bool YMN> cudaError_t launch_nt(const Problem &p, c
   k.tiles_per_batch = (p.M + TILE - 1) / TILE;
   k.total_tiles = k.tiles_per_batch * p.B;
   k.nchunks = (TILE + 2 * p.w + CHUNK - 1) / CHUNK;
-  k.paired = (p.w % 64 == 0) ? 1 : 0;
+  k.paired = PAIRED ? 1 : 0;
+  k.dbg = 0;
+#ifdef WMM_TRACE
+  if (const char *d = getenv("WMM_DBG")) k.dbg = atoi(d);
+#endif
   k.band = p.o;
-  auto kern = band_nt_tc_kernel<BF16, NH, YMN>;
+  auto kern = band_nt_tc_kernel<BF16, NH, YMN, PAIRED>;
   // the attribute is per device; setting it on every call is cheap and needs no per-device cache
   cudaError_t attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::ALLOC);
   if (attr_err != cudaSuccess) {
@@ -243,14 +300,18 @@ template <bool BF16, int NH, bool YMN> cudaError_t launch_nt(const Problem &p, c
     return cudaErrorInvalidValue;
   const int grid = persistent_grid(k.total_tiles);
   set_launch_detail("band_nt launch, grid %d", grid);
-  kern<<<grid, NT_THREADS, S::ALLOC, stream>>>(mx, my, mb, k);
-  return cudaGetLastError();
+  return launch_pdl(kern, grid, NT_THREADS, S::ALLOC, stream, mx, my, mb, k);
 }
 
 template <int NH> cudaError_t launch_nt_any(const Problem &p, cudaStream_t stream) {
   const bool bf16 = p.dtype == WMM_BF16;
-  if (y_position_major(p)) return bf16 ? launch_nt<true, NH, true>(p, stream) : launch_nt<false, NH, true>(p, stream);
-  return bf16 ? launch_nt<true, NH, false>(p, stream) : launch_nt<false, NH, false>(p, stream);
+  const bool paired = (p.w % 64) == 0;   // 2w a multiple of 128
+  if (y_position_major(p)) {
+    if (paired) return bf16 ? launch_nt<true, NH, true, true>(p, stream) : launch_nt<false, NH, true, true>(p, stream);
+    return bf16 ? launch_nt<true, NH, true, false>(p, stream) : launch_nt<false, NH, true, false>(p, stream);
+  }
+  if (paired) return bf16 ? launch_nt<true, NH, false, true>(p, stream) : launch_nt<false, NH, false, true>(p, stream);
+  return bf16 ? launch_nt<true, NH, false, false>(p, stream) : launch_nt<false, NH, false, false>(p, stream);
 }
 
 // MODE 0 / 1: one problem (band_n / band_t).  MODE 2: `p` is the band_n problem and `pt` the band_t
@@ -291,8 +352,7 @@ template <bool BF16, int NH, int MODE, bool YMN> cudaError_t launch_mm(const Pro
   int grid = persistent_grid(items);
   if (MODE == 2 && (grid & 1) && grid > 1) --grid;  // even: each CTA keeps to one of the two passes
   set_launch_detail("band_mm mode %d launch, grid %d", MODE, grid);
-  kern<<<grid, MM_THREADS, S::ALLOC, stream>>>(mband, mother0, mout0, mother1, mout1, k);
-  return cudaGetLastError();
+  return launch_pdl(kern, grid, MM_THREADS, S::ALLOC, stream, mband, mother0, mout0, mother1, mout1, k);
 }
 
 template <int MODE, bool YMN> cudaError_t launch_mm_n(const Problem &p, const Problem *pt, cudaStream_t stream) {
@@ -345,8 +405,7 @@ template <bool BF16, int NH> cudaError_t launch_sweep(const Problem &pn, const P
     return cudaErrorInvalidValue;
   const int grid = persistent_grid(k.total_rows);
   set_launch_detail("band_bwd_sweep launch, grid %d", grid);
-  kern<<<grid, SWP_THREADS, S::ALLOC, stream>>>(mband, my, mx, k);
-  return cudaGetLastError();
+  return launch_pdl(kern, grid, SWP_THREADS, S::ALLOC, stream, mband, my, mx, k);
 }
 
 }  // namespace

@@ -93,6 +93,10 @@ band_mm_tc_kernel(const __grid_constant__ CUtensorMap map_band, const __grid_con
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // Everything above (barriers, tensor memory, tensor-map prefetch) may run under the tail of the previous kernel of the
+  // stream; from here on global memory is read and written.
+  griddep_launch_dependents();
+  griddep_wait();
 
   // Work items, identical in every role: item -> (tile, transposed?).
   const int total_items = MODE == 2 ? 2 * p.total_tiles : p.total_tiles;

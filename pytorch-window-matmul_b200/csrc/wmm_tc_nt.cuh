@@ -1,6 +1,8 @@
 // band_nt on tensor cores: Band = band(X Y^T).  Included by wmm_tc.cu (inside namespace wmm::<anon>).
 //
-// One MMA chunk = X tile (128 rows x NH) times 128 rows of Y -> a 128 x 128 fp32 accumulator in TMEM.
+// One MMA chunk = X tile (128 rows x NH) times 128 rows of Y -> a 128 x 128 fp32 accumulator in TMEM, issued as
+// NH / 16 instructions of shape 128 x 128 x 16 (the issuing thread is the scarcest resource of this kernel: an
+// instruction costs it about as much whatever its width, so chunks are not split into narrower MMAs).
 // A tile of 128 band rows needs ceil((128 + 2w) / 128) chunks.  The epilogue turns accumulators into
 // band storage:
 //   * a chunk that lies wholly inside the band is converted, written to a swizzled staging buffer and
@@ -27,6 +29,7 @@ struct NtParams {
   int B, M, w, off, lo, hi;
   int tiles_per_batch, total_tiles, nchunks;
   int paired;  // 2w is a multiple of 128: merge first and last chunk of a tile
+  int dbg;     // (trace builds only) experiment switches
   void *band;
 };
 
@@ -35,10 +38,14 @@ template <int NH> struct NtSmem {
   static constexpr int QS = 2;
   static constexpr int KS = NH >= 128 ? 3 : 4;
   static constexpr int STAGE_HALF = TILE * 128;  // 128 lines x 64 columns x 2 bytes
+  // Staging boxes per epilogue group.  With two, a group converts its next item while the store of the previous one
+  // still waits its turn in the SM's store queue (four groups feed one queue: a store's shared-memory read completes
+  // about a microsecond after it was issued); with one, conversion and queueing add up.
+  static constexpr int STAGE_BUFS = NH >= 128 ? 1 : 2;
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + QS * OT::BYTES;
-  static constexpr int OFF_STAGE = OFF_K + KS * OT::BYTES;  // one 16 KB box per epilogue group
-  static constexpr int OFF_BARS = OFF_STAGE + EPI_GROUPS * STAGE_HALF;
+  static constexpr int OFF_STAGE = OFF_K + KS * OT::BYTES;  // STAGE_BUFS 16 KB boxes per epilogue group
+  static constexpr int OFF_BARS = OFF_STAGE + EPI_GROUPS * STAGE_BUFS * STAGE_HALF;
   static constexpr int NBARS = 2 * QS + 2 * KS + 2 * ACC_STAGES;
   static constexpr int OFF_MISC = OFF_BARS + NBARS * 8;
   static constexpr int BYTES = OFF_MISC + 32;
@@ -74,7 +81,9 @@ __device__ __forceinline__ void mask_columns(uint32_t (&v)[32], int kbase, int k
 // YMN: Y is stored with the POSITIONS contiguous (K of window_matmul given as a contiguous (B, N, M) tensor, as
 // in the reference's README).  A chunk is then two TMA boxes of (64 positions x NH rows), used as an
 // MN-major B operand; otherwise Y rows are contiguous in the hidden index and the operand is K-major.
-template <bool BF16, int NH, bool YMN>
+// PAIRED: 2w is a multiple of 128, so the first and the last chunk of a tile are merged (a compile-time switch: each
+// variant carries only the epilogue paths it can reach, which keeps the loop body small).
+template <bool BF16, int NH, bool YMN, bool PAIRED>
 __global__ void __launch_bounds__(NT_THREADS, 1)
 band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
                   const __grid_constant__ CUtensorMap map_band, const NtParams p) {
@@ -95,7 +104,8 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   volatile int *epi_ok = reinterpret_cast<volatile int *>(base_ptr + S::OFF_MISC + 8);  // one per group
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const bool paired = p.paired != 0;
+  constexpr bool paired = PAIRED;
+  if (threadIdx.x == 0) WMM_TRACE_POINT(0);
   // order in which the chunks of a tile are loaded and multiplied: with pairing the last chunk comes
   // second, so that both triangles are in TMEM together
   auto chunk_at = [&](int k) -> int { return !paired ? k : (k == 0 ? 0 : (k == 1 ? p.nchunks - 1 : k - 1)); };
@@ -103,7 +113,7 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::QS; s++) { mbar_init(bar_q_full(s), 1); mbar_init(bar_q_empty(s), 1); }
     for (int s = 0; s < S::KS; s++) { mbar_init(bar_k_full(s), 1); mbar_init(bar_k_empty(s), 1); }
-    for (int s = 0; s < ACC_STAGES; s++) { mbar_init(bar_acc_full(s), 1); mbar_init(bar_acc_empty(s), EPI_THREADS); }
+    for (int s = 0; s < ACC_STAGES; s++) { mbar_init(bar_acc_full(s), 1); mbar_init(bar_acc_empty(s), 2 * EPI_THREADS); }
     *abort_flag = 0;
     for (int g = 0; g < EPI_GROUPS; g++) epi_ok[g] = 1;
     fence_mbar_init();
@@ -119,23 +129,36 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // Everything above (barriers, tensor memory, tensor-map prefetch) may run under the tail of the previous kernel of the
+  // stream; from here on global memory is read and written.
+  if (threadIdx.x == 0) WMM_TRACE_POINT(1);
+  griddep_launch_dependents();
+  griddep_wait();
+  if (threadIdx.x == 0) WMM_TRACE_POINT(2);
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       int qit = 0, kit = 0;
       bool ok = true;
+      unsigned long long w_qe = 0, w_ke = 0;   // (trace builds) time spent waiting for free stages
+      (void)w_qe; (void)w_ke;
       for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x, ++qit) {
         const int b = tile / p.tiles_per_batch, r0 = (tile % p.tiles_per_batch) * TILE;
         const int qs = qit % S::QS;
+        WMM_TRACE_T0(t_qe);
         if (!(ok = mbar_wait(bar_q_empty(qs), ((qit / S::QS) & 1) ^ 1, abort_flag))) break;
+        WMM_TRACE_ACC(w_qe, t_qe);
         mbar_expect_tx(bar_q_full(qs), OT::BYTES);
 #pragma unroll
         for (int bx = 0; bx < OT::NBOX; bx++)
           tma_load_3d(base + S::OFF_Q + qs * OT::BYTES + bx * OT::BOX_BYTES, &map_x, bar_q_full(qs), bx * OT::BOXK, r0, b);
+        if (qit == 0) WMM_TRACE_POINT(3);
         for (int k = 0; k < p.nchunks; ++k, ++kit) {
           const int ks = kit % S::KS;
+          WMM_TRACE_T0(t_ke);
           if (!(ok = mbar_wait(bar_k_empty(ks), ((kit / S::KS) & 1) ^ 1, abort_flag))) break;
+          WMM_TRACE_ACC(w_ke, t_ke);
           mbar_expect_tx(bar_k_full(ks), OT::BYTES);
           const int p0 = r0 - p.w + p.off + chunk_at(k) * CHUNK;
           if (YMN) {
@@ -149,45 +172,58 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           }
         }
       }
+      WMM_TRACE_POINT(4);
+      WMM_TRACE_STORE(26, w_qe);
+      WMM_TRACE_STORE(27, w_ke);
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
-    // One accumulator stage = half a chunk (128 rows x 64 positions, 64 TMEM columns), the unit the
-    // epilogue groups consume; 8 stages.  With pairing the first and last chunk are interleaved half by
-    // half, so that each merged half-box finds both its triangles in TMEM.
+    // One accumulator stage = one chunk (128 rows x 128 positions, 128 TMEM columns); 4 stages.  The two halves of a
+    // stage are converted by two epilogue groups; the stage is free again when both have read it.  With pairing the
+    // first and the last chunk of a tile are multiplied back to back, so that both triangles are in TMEM together.
     if (lane == 0) {
-      constexpr uint32_t IDESC = instr_desc_f16(BF16, false, YMN, TILE, HALF);
+      constexpr uint32_t IDESC = instr_desc_f16(BF16, false, YMN, TILE, CHUNK);
       // MN-major Y: one box = NH rows (hidden) of 64 positions (128 B); 8-row groups 1024 B apart, a k-step of
-      // 16 hidden rows is 2048 B further; the second 64 positions of the chunk are the second box.
+      // 16 hidden rows is 2048 B further; the second 64 positions of the chunk are the second box (leading offset).
       constexpr uint64_t YDESC = YMN ? smem_desc_base(OT::BYTES / 2, 1024, 2u) : OT::DESC;
       int qit = 0, kit = 0, ait = 0;
       bool ok = true;
-      auto half_mma = [&](uint32_t q_addr, uint32_t k_addr, int half) -> bool {
+      unsigned long long w_qf = 0, w_kf = 0, w_ae = 0, w_is = 0, w_cm = 0;   // (trace builds) waits; time issuing MMAs / commits
+      (void)w_qf; (void)w_kf; (void)w_ae; (void)w_is; (void)w_cm;
+      auto chunk_mma = [&](uint32_t q_addr, uint32_t k_addr) -> bool {
         const int as = ait % ACC_STAGES;
+        WMM_TRACE_T0(t_ae);
         if (!mbar_wait(bar_acc_empty(as), ((ait / ACC_STAGES) & 1) ^ 1, abort_flag)) return false;
+        WMM_TRACE_ACC(w_ae, t_ae);
         tc_fence_after_sync();
-        // K-major: rows 64*half .. of every box; MN-major: box `half`
-        const uint32_t b_addr = k_addr + (YMN ? half * (OT::BYTES / 2) : half * HALF * OT::SW_BYTES);
+        WMM_TRACE_T0(t_is);
 #pragma unroll
         for (int s = 0; s < OT::KSTEPS; s++)
-          umma_f16(tmem_base + as * HALF, smem_desc(OT::DESC, q_addr + OT::kstep_offset(s)),
-                   smem_desc(YDESC, b_addr + (YMN ? (uint32_t)s * 2048u : OT::kstep_offset(s))), IDESC, s > 0 ? 1u : 0u);
+          umma_f16(tmem_base + as * CHUNK, smem_desc(OT::DESC, q_addr + OT::kstep_offset(s)),
+                   smem_desc(YDESC, k_addr + (YMN ? (uint32_t)s * 2048u : OT::kstep_offset(s))), IDESC, s > 0 ? 1u : 0u);
+        WMM_TRACE_ACC(w_is, t_is);
+        WMM_TRACE_T0(t_cm);
         umma_commit(bar_acc_full(as));
+        WMM_TRACE_ACC(w_cm, t_cm);
         ++ait;
         return true;
       };
       for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x, ++qit) {
         const int qs = qit % S::QS;
+        WMM_TRACE_T0(t_qf);
         if (!(ok = mbar_wait(bar_q_full(qs), (qit / S::QS) & 1, abort_flag))) break;
+        WMM_TRACE_ACC(w_qf, t_qf);
+        if (qit == 0) WMM_TRACE_POINT(5);
         const uint32_t q_addr = base + S::OFF_Q + qs * OT::BYTES;
         int k = 0;
         if (paired) {
           const int ks0 = kit % S::KS, ks1 = (kit + 1) % S::KS;
+          WMM_TRACE_T0(t_kf);
           if (!(ok = mbar_wait(bar_k_full(ks0), (kit / S::KS) & 1, abort_flag))) break;
           if (!(ok = mbar_wait(bar_k_full(ks1), ((kit + 1) / S::KS) & 1, abort_flag))) break;
+          WMM_TRACE_ACC(w_kf, t_kf);
           const uint32_t k0_addr = base + S::OFF_K + ks0 * OT::BYTES, k1_addr = base + S::OFF_K + ks1 * OT::BYTES;
-          for (int half = 0; ok && half < 2; half++) ok = half_mma(q_addr, k0_addr, half) && half_mma(q_addr, k1_addr, half);
-          if (!ok) break;
+          if (!(ok = chunk_mma(q_addr, k0_addr) && chunk_mma(q_addr, k1_addr))) break;
           umma_commit(bar_k_empty(ks0));
           umma_commit(bar_k_empty(ks1));
           kit += 2;
@@ -195,13 +231,21 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         }
         for (; k < p.nchunks; ++k, ++kit) {
           const int ks = kit % S::KS;
+          WMM_TRACE_T0(t_kf);
           if (!(ok = mbar_wait(bar_k_full(ks), (kit / S::KS) & 1, abort_flag))) break;
+          WMM_TRACE_ACC(w_kf, t_kf);
           const uint32_t k_addr = base + S::OFF_K + ks * OT::BYTES;
-          if (!(ok = half_mma(q_addr, k_addr, 0) && half_mma(q_addr, k_addr, 1))) break;
+          if (!(ok = chunk_mma(q_addr, k_addr))) break;
           umma_commit(bar_k_empty(ks));
         }
         if (ok) umma_commit(bar_q_empty(qs));
       }
+      WMM_TRACE_POINT(6);
+      WMM_TRACE_STORE(23, w_qf);
+      WMM_TRACE_STORE(24, w_kf);
+      WMM_TRACE_STORE(25, w_ae);
+      WMM_TRACE_STORE(28, w_is);
+      WMM_TRACE_STORE(29, w_cm);
     }
   } else {
     // ---------------- epilogue groups: thread <-> band row of the tile ----------------
@@ -212,49 +256,90 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     const int rr = quarter * 32 + lane;
     const bool leader = (threadIdx.x == 64 + grp * EPI_THREADS);
     const uint32_t bar_id = 1 + grp;
-    const uint32_t stage = base + S::OFF_STAGE + grp * S::STAGE_HALF;
+    const uint32_t stage0 = base + S::OFF_STAGE + grp * (S::STAGE_BUFS * S::STAGE_HALF);
+    int own = 0;   // items this group has staged so far: picks the staging box
     const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
     const int W = 2 * p.w + 1;
     const int items_per_tile = 2 * (paired ? p.nchunks - 1 : p.nchunks);
     uint16_t *band = static_cast<uint16_t *>(p.band);
-    int ait = 0, iit = 0;  // accumulator stages consumed so far / half-chunk items seen so far (all groups)
+    int cit = 0, iit = 0, rot = 0;  // chunks (accumulator stages) of earlier tiles / half-chunk items seen so far / group rotation
+    unsigned long long w_af = 0, w_st = 0, w_cv = 0, n_items = 0;   // (trace builds) leader: waits, conversion time, items
+    (void)w_af; (void)w_st; (void)w_cv; (void)n_items;
+    int tl = 0;   // (trace builds) own items so far: group 0's leader records a timeline of its first 16 items
+    (void)tl;
+#define NT_TL(k) do { if (leader && grp == 0 && tl < 12) WMM_TRACE_STORE(32 + 10 * tl + (k), (unsigned long long)clock64()); } while (0)
+    int skips = 0; (void)skips;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
       const int b = tile / p.tiles_per_batch, r0 = (tile % p.tiles_per_batch) * TILE;
       const int i = r0 + rr;
       const int vr = min(TILE, p.M - r0);  // valid rows of this tile
       const bool rows_ok = rr < vr;
-      for (int hitem = 0; hitem < items_per_tile; ++hitem, ++iit) {
+      // Items go to the groups round-robin over the CTA's whole item sequence, shifted by two from tile to tile so that
+      // the merged items (the costly ones, always the first two of a tile) do not always land on the same two groups.
+      // A group visits only its own items: the loop body is large, and an iteration that merely skips an item still
+      // costs two jumps across it.
+      const int tile_iit = iit;   // items of earlier tiles
+      for (int hitem = (grp - tile_iit - rot) & (EPI_GROUPS - 1); hitem < items_per_tile; hitem += EPI_GROUPS) {
         const int item = hitem >> 1, h = hitem & 1;
         const bool pair_item = paired && item == 0;
-        const int a0 = ait;
-        ait += pair_item ? 2 : 1;
-        if ((iit % EPI_GROUPS) != grp) continue;
+        // stage of this item's chunk: with pairing the tile's stages hold chunks 0, last, 1, 2, ... in this order
+        const int a0 = cit + (paired ? (item == 0 ? 0 : item + 1) : item);
         const int as = a0 % ACC_STAGES, as2 = (a0 + 1) % ACC_STAGES;
+        const uint32_t stage = stage0 + (uint32_t)(own % S::STAGE_BUFS) * S::STAGE_HALF;
         const int c = pair_item ? 0 : item;  // chunk index (with pairing, items 1.. are chunks 1..)
         const bool staged = pair_item || ((c >= 1) && (c * CHUNK + CHUNK - 1 <= 2 * p.w));
+        NT_TL(0);
         if (leader) {
+          WMM_TRACE_T0(t_af);
           int good = mbar_wait(bar_acc_full(as), (a0 / ACC_STAGES) & 1, abort_flag) ? 1 : 0;
           if (good && pair_item) good = mbar_wait(bar_acc_full(as2), ((a0 + 1) / ACC_STAGES) & 1, abort_flag) ? 1 : 0;
-          if (staged) bulk_wait_read<0>();  // this group's previous store has drained its staging buffer
+          WMM_TRACE_ACC(w_af, t_af);
+          NT_TL(1);
+          if (grp == 0 && iit == 0) WMM_TRACE_POINT(7);
+          WMM_TRACE_T0(t_st);
+          if (staged) bulk_wait_read<S::STAGE_BUFS - 1>();  // the store that last used this staging box has drained it
+          WMM_TRACE_ACC(w_st, t_st);
+          NT_TL(2);
           epi_ok[grp] = good;
         }
         named_bar_sync(bar_id, EPI_THREADS);
+        NT_TL(3);
+        WMM_TRACE_T0(t_cv);
         if (!(ok = (epi_ok[grp] != 0))) break;
         tc_fence_after_sync();
-        const uint32_t taddr = tmem_base + as * HALF + lane_sel;  // columns 64*h .. of chunk c
+        const uint32_t taddr = tmem_base + as * CHUNK + h * HALF + lane_sel;  // columns 64*h .. of chunk c
         // positions of chunk c inside the sequence: columns kk in [kk_lo, kk_hi)
         const int p0 = r0 - p.w + p.off + c * CHUNK;
         const int kk_lo = p.lo - p0, kk_hi = p.hi - p0;
         const bool edge = kk_lo > 0 || kk_hi < CHUNK;
 
-        if (pair_item) {
+#ifdef WMM_TRACE
+        if (p.dbg & 2) {   // experiment: no conversion at all
+          tc_fence_before_sync();
+          mbar_arrive(bar_acc_empty(as));
+          if (pair_item) mbar_arrive(bar_acc_empty(as2));
+        } else if (pair_item && (p.dbg & 4)) {   // experiment: pair items at the cost of plain ones
+          uint32_t va[32], vb[32];
+          tmem_ld_x32(taddr, va);
+          tmem_ld_x32(taddr + 32, vb);
+          tmem_ld_wait();
+#pragma unroll
+          for (int q4 = 0; q4 < 4; q4++) st_shared_v4(stage_addr(stage, rr, q4), pack8<BF16>(&va[q4 * 8]));
+#pragma unroll
+          for (int q4 = 0; q4 < 4; q4++) st_shared_v4(stage_addr(stage, rr, 4 + q4), pack8<BF16>(&vb[q4 * 8]));
+          tc_fence_before_sync();
+          mbar_arrive(bar_acc_empty(as));
+          mbar_arrive(bar_acc_empty(as2));
+        } else
+#endif
+        if (PAIRED && pair_item) {
           // ---- merged first + last chunk ----
           // A warp owns rows 32*quarter .. +31.  Column blocks left of its diagonal block hold only
           // last-chunk entries of these rows, blocks right of it only first-chunk entries; the diagonal
           // block holds both, split per lane.
           const int cl = p.nchunks - 1;
-          const uint32_t taddr_l = tmem_base + as2 * HALF + lane_sel;
+          const uint32_t taddr_l = tmem_base + as2 * CHUNK + h * HALF + lane_sel;
           const int kl_lo = kk_lo - cl * CHUNK, kl_hi = kk_hi - cl * CHUNK;
           const bool edge_l = kl_lo > 0 || kl_hi < CHUNK;
           const bool direct_l = (rr == vr - 1);  // last valid row: its last-chunk piece has no staging line
@@ -338,6 +423,10 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           tmem_ld_x32(taddr, va);
           tmem_ld_x32(taddr + 32, vb);
           tmem_ld_wait();
+          // the values are in registers: the accumulator half is free for the next chunk before the conversion starts
+          tc_fence_before_sync();
+          mbar_arrive(bar_acc_empty(as));
+          NT_TL(4);
           if (edge) {
             mask_columns(va, h * 64, kk_lo, kk_hi);
             mask_columns(vb, h * 64 + 32, kk_lo, kk_hi);
@@ -346,9 +435,8 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           for (int q4 = 0; q4 < 4; q4++) st_shared_v4(stage_addr(stage, rr, q4), pack8<BF16>(&va[q4 * 8]));
 #pragma unroll
           for (int q4 = 0; q4 < 4; q4++) st_shared_v4(stage_addr(stage, rr, 4 + q4), pack8<BF16>(&vb[q4 * 8]));
-          tc_fence_before_sync();
-          mbar_arrive(bar_acc_empty(as));
-        } else {
+          NT_TL(5);
+        } else if (!PAIRED) {
           // ---- triangular / ragged chunk of an unpaired window: predicated stores from registers.
           // Groups of 8 columns start on 16-byte boundaries of the band tensor, so whole groups go out
           // as one 16-byte store.
@@ -381,14 +469,38 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         if (staged) {
           fence_proxy_async_smem();
           named_bar_sync(bar_id, EPI_THREADS);
+          NT_TL(6);
           if (leader) {
-            tma_store_3d(&map_band, stage, r0 + c * CHUNK + h * 64, r0, b);  // x = i + j of the box's first column
-            bulk_commit();
+            WMM_TRACE_ACC(w_cv, t_cv);
+            ++n_items;
+#ifdef WMM_TRACE
+            if (!(p.dbg & 1))
+#endif
+            {
+              tma_store_3d(&map_band, stage, r0 + c * CHUNK + h * 64, r0, b);  // x = i + j of the box's first column
+              bulk_commit();
+            }
+            if (grp == 0 && iit == 0) WMM_TRACE_POINT(8);
           }
         }
+        if (staged) ++own;
+        NT_TL(7);
+        ++tl;
+        skips = 0;
       }
+      cit += p.nchunks;
+      iit += items_per_tile;
+      rot += 2;
+    }
+    if (leader && grp == 0) WMM_TRACE_POINT(9);
+    if (leader && (grp == 0 || grp == 2)) {
+      WMM_TRACE_STORE(13 + 2 * grp, w_af);
+      WMM_TRACE_STORE(14 + 2 * grp, w_st);
+      WMM_TRACE_STORE(15 + 2 * grp, w_cv);
+      WMM_TRACE_STORE(16 + 2 * grp, n_items);
     }
     if (leader) bulk_wait_all();
+    if (leader && grp == 0) WMM_TRACE_POINT(10);
   }
 
   // ---------------- teardown ----------------
@@ -401,8 +513,10 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
     __syncthreads();
   }
+  if (threadIdx.x == 0) WMM_TRACE_POINT(11);
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
+    if (lane == 0) WMM_TRACE_POINT(12);
   }
 }

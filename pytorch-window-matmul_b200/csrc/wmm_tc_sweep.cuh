@@ -111,6 +111,7 @@ band_bwd_sweep_kernel(const __grid_constant__ CUtensorMap map_band, const __grid
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nslots = 2 * p.D + 2;
+  if (threadIdx.x == 0) WMM_TRACE_POINT(0);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::STAGES; s++) {
@@ -143,6 +144,10 @@ band_bwd_sweep_kernel(const __grid_constant__ CUtensorMap map_band, const __grid
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // Everything above (barriers, tensor memory, tensor-map prefetch) may run under the tail of the previous kernel of the
+  // stream; from here on global memory is read and written.
+  griddep_launch_dependents();
+  griddep_wait();
   // tensor memory columns: row accumulators at 0 and NH, column slot s at (2 + s) NH
   auto tmem_row = [&](int as) { return tmem_base + (uint32_t)(as * NH); };
   auto tmem_col = [&](int slot) { return tmem_base + (uint32_t)((2 + slot) * NH); };
@@ -206,6 +211,9 @@ band_bwd_sweep_kernel(const __grid_constant__ CUtensorMap map_band, const __grid
       int it = 0, xrow = 0, nrow = 0, since = 0;
       uint32_t mk_bits = 0, col_bits = 0;   // parity of: masked-barrier uses per stage; column-slot uses
       int as = 0, xb = 0;
+      unsigned long long w_wait = 0, w_issue = 0;   // (trace builds) time in waits / issuing MMAs and commits
+      (void)w_wait; (void)w_issue;
+      WMM_TRACE_POINT(1);
       sweep_walk(
           p,
           [&](int, int, bool warm) {
@@ -221,6 +229,7 @@ band_bwd_sweep_kernel(const __grid_constant__ CUtensorMap map_band, const __grid
           },
           [&](int, int r, int pt, bool warm, bool t_pass, bool first_in_row) {
             const int s = it % S::STAGES;
+            WMM_TRACE_T0(t_w);
             if (!mbar_wait(bar_full(s), (it / S::STAGES) & 1, abort_flag)) return false;
             if (mask_sync(box_plain(r, pt), since)) {
               if (!mbar_wait(bar_masked(s), (mk_bits >> s) & 1u, abort_flag)) return false;
@@ -233,6 +242,8 @@ band_bwd_sweep_kernel(const __grid_constant__ CUtensorMap map_band, const __grid
               if (!mbar_wait(bar_tempty(slot), ((col_bits >> slot) & 1u) ^ 1u, abort_flag)) return false;
               col_bits ^= 1u << slot;
             }
+            WMM_TRACE_ACC(w_wait, t_w);
+            WMM_TRACE_T0(t_i);
             tc_fence_after_sync();
             const uint32_t a_addr = base + s * S::STAGE_BYTES, y_addr = a_addr + BT::BYTES;
             const uint32_t x_addr = base + S::OFF_X + xb * OT::BYTES;
@@ -249,6 +260,7 @@ band_bwd_sweep_kernel(const __grid_constant__ CUtensorMap map_band, const __grid
                          smem_desc(BDESC, x_addr + (uint32_t)k * 16u * OT::SW_BYTES), IDESC_T, (!col_first || k > 0) ? 1u : 0u);
             }
             umma_commit(bar_empty(s));
+            WMM_TRACE_ACC(w_issue, t_i);
             return true;
           },
           [&](int, int pt) {
@@ -263,6 +275,9 @@ band_bwd_sweep_kernel(const __grid_constant__ CUtensorMap map_band, const __grid
             umma_commit(bar_xempty(xb));
             return true;
           });
+      WMM_TRACE_POINT(2);
+      WMM_TRACE_STORE(3, w_wait);
+      WMM_TRACE_STORE(4, w_issue);
     }
   } else if (warp < 6) {
     // ---------------- mask warps: thread <-> row of the band box ----------------

@@ -10,7 +10,8 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libwmm_b200.so")
+# WMM_B200_LIBRARY may name a variant build of the same ABI (e.g. one compiled with -DWMM_TRACE for kernel timelines).
+LIB_PATH = os.environ.get("WMM_B200_LIBRARY") or os.path.join(_HERE, "libwmm_b200.so")
 
 F16, BF16, F32, F64 = 0, 1, 2, 3
 FLAG_SPLIT_ROUNDING = 1 << 0
