@@ -278,10 +278,6 @@ template <bool BF16, int NH, bool YMN, bool PAIRED> cudaError_t launch_nt(const 
   k.total_tiles = k.tiles_per_batch * p.B;
   k.nchunks = (TILE + 2 * p.w + CHUNK - 1) / CHUNK;
   k.paired = PAIRED ? 1 : 0;
-  k.dbg = 0;
-#ifdef WMM_TRACE
-  if (const char *d = getenv("WMM_DBG")) k.dbg = atoi(d);
-#endif
   k.band = p.o;
   auto kern = band_nt_tc_kernel<BF16, NH, YMN, PAIRED>;
   // the attribute is per device; setting it on every call is cheap and needs no per-device cache

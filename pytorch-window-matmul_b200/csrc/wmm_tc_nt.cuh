@@ -15,21 +15,22 @@
 //   * for other windows the triangular chunks are written with predicated 16-byte stores from registers.
 //
 // Warps: 0 = TMA producer, 1 = MMA issuer / TMEM owner, 2-17 = four epilogue groups of four warps that
-// take work items (half a chunk = one 128 x 64 TMA box) round-robin, each with its own staging box: the
-// conversion is latency-bound per warp, so it needs many warps, and one group's conversion overlaps the
-// drain of the others' stores.
+// take work items (half a chunk = one 128 x 64 TMA box) round-robin, each with its own staging boxes: the
+// conversion is latency-bound per warp, so it needs many warps.  Warp 18 = store issuer: it alone issues the TMA
+// stores of all groups, in item order, and hands a staging box back once its store has read it.  (Issuing a
+// tensor store holds the issuing thread for a few hundred nanoseconds; done by the groups' own threads that time
+// sat on every item's critical path.)
 
 constexpr int HALF = 64;        // positions per accumulator stage / per epilogue work item
 constexpr int EPI_GROUPS = 4;
 constexpr int EPI_THREADS = 128;
-constexpr int NT_THREADS = 64 + EPI_GROUPS * EPI_THREADS;
+constexpr int NT_THREADS = 64 + EPI_GROUPS * EPI_THREADS + 32;
 constexpr unsigned long long ST_NT_TIMEOUT = 1ull << 0;
 
 struct NtParams {
   int B, M, w, off, lo, hi;
   int tiles_per_batch, total_tiles, nchunks;
   int paired;  // 2w is a multiple of 128: merge first and last chunk of a tile
-  int dbg;     // (trace builds only) experiment switches
   void *band;
 };
 
@@ -38,17 +39,18 @@ template <int NH> struct NtSmem {
   static constexpr int QS = 2;
   static constexpr int KS = NH >= 128 ? 3 : 4;
   static constexpr int STAGE_HALF = TILE * 128;  // 128 lines x 64 columns x 2 bytes
-  // Staging boxes per epilogue group.  With two, a group converts its next item while the store of the previous one
-  // still waits its turn in the SM's store queue (four groups feed one queue: a store's shared-memory read completes
-  // about a microsecond after it was issued); with one, conversion and queueing add up.
-  static constexpr int STAGE_BUFS = NH >= 128 ? 1 : 2;
+  // Staging boxes: a pool shared by the four epilogue groups, used in item order (item n of the CTA goes through box
+  // n % STAGE_BOXES).  With more boxes than groups a group converts its next item while the stores of earlier ones
+  // still wait their turn in the SM's store queue.
+  static constexpr int STAGE_BOXES = NH >= 128 ? 4 : 8;
+  static constexpr int STORE_DEPTH = STAGE_BOXES / 2;   // stores whose shared-memory read may be pending when the next is issued
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + QS * OT::BYTES;
-  static constexpr int OFF_STAGE = OFF_K + KS * OT::BYTES;  // STAGE_BUFS 16 KB boxes per epilogue group
-  static constexpr int OFF_BARS = OFF_STAGE + EPI_GROUPS * STAGE_BUFS * STAGE_HALF;
-  static constexpr int NBARS = 2 * QS + 2 * KS + 2 * ACC_STAGES;
+  static constexpr int OFF_STAGE = OFF_K + KS * OT::BYTES;  // STAGE_BOXES boxes of 16 KB
+  static constexpr int OFF_BARS = OFF_STAGE + STAGE_BOXES * STAGE_HALF;
+  static constexpr int NBARS = 2 * QS + 2 * KS + 2 * ACC_STAGES + 2 * STAGE_BOXES;
   static constexpr int OFF_MISC = OFF_BARS + NBARS * 8;
-  static constexpr int BYTES = OFF_MISC + 32;
+  static constexpr int BYTES = OFF_MISC + 64;
   static constexpr int ALLOC = BYTES + 1024;  // slack to align the base to 1024 B
 };
 
@@ -99,9 +101,12 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   auto bar_k_empty = [&](int s) { return bars + 8u * (2 * S::QS + S::KS + s); };
   auto bar_acc_full = [&](int s) { return bars + 8u * (2 * S::QS + 2 * S::KS + s); };
   auto bar_acc_empty = [&](int s) { return bars + 8u * (2 * S::QS + 2 * S::KS + ACC_STAGES + s); };
+  // staging box x: filled by an epilogue group (all its threads arrive), handed back by the store issuer
+  auto bar_st_full = [&](int x) { return bars + 8u * (2 * S::QS + 2 * S::KS + 2 * ACC_STAGES + x); };
+  auto bar_st_free = [&](int x) { return bars + 8u * (2 * S::QS + 2 * S::KS + 2 * ACC_STAGES + S::STAGE_BOXES + x); };
   volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + S::OFF_MISC);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(base_ptr + S::OFF_MISC + 4);
-  volatile int *epi_ok = reinterpret_cast<volatile int *>(base_ptr + S::OFF_MISC + 8);  // one per group
+  volatile int *epi_ok = reinterpret_cast<volatile int *>(base_ptr + S::OFF_MISC + 8);  // two per group, used in turn
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr bool paired = PAIRED;
@@ -110,12 +115,19 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   // second, so that both triangles are in TMEM together
   auto chunk_at = [&](int k) -> int { return !paired ? k : (k == 0 ? 0 : (k == 1 ? p.nchunks - 1 : k - 1)); };
 
+  // Items of a tile whose box lies wholly inside the band go through a staging box and a TMA store: all of them with
+  // pairing; otherwise the halves of chunks 1 .. floor((2w - 127) / 128).  They are consecutive: items st_first ..
+  // st_first + st_count - 1 of every tile.
+  const int st_first = paired ? 0 : 2;
+  const int st_count = paired ? 2 * (p.nchunks - 1) : 2 * max(0, (2 * p.w - (CHUNK - 1)) / CHUNK);
+
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::QS; s++) { mbar_init(bar_q_full(s), 1); mbar_init(bar_q_empty(s), 1); }
     for (int s = 0; s < S::KS; s++) { mbar_init(bar_k_full(s), 1); mbar_init(bar_k_empty(s), 1); }
     for (int s = 0; s < ACC_STAGES; s++) { mbar_init(bar_acc_full(s), 1); mbar_init(bar_acc_empty(s), 2 * EPI_THREADS); }
+    for (int x = 0; x < S::STAGE_BOXES; x++) { mbar_init(bar_st_full(x), EPI_THREADS); mbar_init(bar_st_free(x), 1); }
     *abort_flag = 0;
-    for (int g = 0; g < EPI_GROUPS; g++) epi_ok[g] = 1;
+    for (int g = 0; g < 2 * EPI_GROUPS; g++) epi_ok[g] = 1;
     fence_mbar_init();
     prefetch_tmap(&map_x);
     prefetch_tmap(&map_y);
@@ -141,14 +153,10 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     if (lane == 0) {
       int qit = 0, kit = 0;
       bool ok = true;
-      unsigned long long w_qe = 0, w_ke = 0;   // (trace builds) time spent waiting for free stages
-      (void)w_qe; (void)w_ke;
       for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x, ++qit) {
         const int b = tile / p.tiles_per_batch, r0 = (tile % p.tiles_per_batch) * TILE;
         const int qs = qit % S::QS;
-        WMM_TRACE_T0(t_qe);
         if (!(ok = mbar_wait(bar_q_empty(qs), ((qit / S::QS) & 1) ^ 1, abort_flag))) break;
-        WMM_TRACE_ACC(w_qe, t_qe);
         mbar_expect_tx(bar_q_full(qs), OT::BYTES);
 #pragma unroll
         for (int bx = 0; bx < OT::NBOX; bx++)
@@ -156,9 +164,7 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         if (qit == 0) WMM_TRACE_POINT(3);
         for (int k = 0; k < p.nchunks; ++k, ++kit) {
           const int ks = kit % S::KS;
-          WMM_TRACE_T0(t_ke);
           if (!(ok = mbar_wait(bar_k_empty(ks), ((kit / S::KS) & 1) ^ 1, abort_flag))) break;
-          WMM_TRACE_ACC(w_ke, t_ke);
           mbar_expect_tx(bar_k_full(ks), OT::BYTES);
           const int p0 = r0 - p.w + p.off + chunk_at(k) * CHUNK;
           if (YMN) {
@@ -173,8 +179,6 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         }
       }
       WMM_TRACE_POINT(4);
-      WMM_TRACE_STORE(26, w_qe);
-      WMM_TRACE_STORE(27, w_ke);
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
@@ -188,40 +192,28 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       constexpr uint64_t YDESC = YMN ? smem_desc_base(OT::BYTES / 2, 1024, 2u) : OT::DESC;
       int qit = 0, kit = 0, ait = 0;
       bool ok = true;
-      unsigned long long w_qf = 0, w_kf = 0, w_ae = 0, w_is = 0, w_cm = 0;   // (trace builds) waits; time issuing MMAs / commits
-      (void)w_qf; (void)w_kf; (void)w_ae; (void)w_is; (void)w_cm;
       auto chunk_mma = [&](uint32_t q_addr, uint32_t k_addr) -> bool {
         const int as = ait % ACC_STAGES;
-        WMM_TRACE_T0(t_ae);
         if (!mbar_wait(bar_acc_empty(as), ((ait / ACC_STAGES) & 1) ^ 1, abort_flag)) return false;
-        WMM_TRACE_ACC(w_ae, t_ae);
         tc_fence_after_sync();
-        WMM_TRACE_T0(t_is);
 #pragma unroll
         for (int s = 0; s < OT::KSTEPS; s++)
           umma_f16(tmem_base + as * CHUNK, smem_desc(OT::DESC, q_addr + OT::kstep_offset(s)),
                    smem_desc(YDESC, k_addr + (YMN ? (uint32_t)s * 2048u : OT::kstep_offset(s))), IDESC, s > 0 ? 1u : 0u);
-        WMM_TRACE_ACC(w_is, t_is);
-        WMM_TRACE_T0(t_cm);
         umma_commit(bar_acc_full(as));
-        WMM_TRACE_ACC(w_cm, t_cm);
         ++ait;
         return true;
       };
       for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x, ++qit) {
         const int qs = qit % S::QS;
-        WMM_TRACE_T0(t_qf);
         if (!(ok = mbar_wait(bar_q_full(qs), (qit / S::QS) & 1, abort_flag))) break;
-        WMM_TRACE_ACC(w_qf, t_qf);
         if (qit == 0) WMM_TRACE_POINT(5);
         const uint32_t q_addr = base + S::OFF_Q + qs * OT::BYTES;
         int k = 0;
         if (paired) {
           const int ks0 = kit % S::KS, ks1 = (kit + 1) % S::KS;
-          WMM_TRACE_T0(t_kf);
           if (!(ok = mbar_wait(bar_k_full(ks0), (kit / S::KS) & 1, abort_flag))) break;
           if (!(ok = mbar_wait(bar_k_full(ks1), ((kit + 1) / S::KS) & 1, abort_flag))) break;
-          WMM_TRACE_ACC(w_kf, t_kf);
           const uint32_t k0_addr = base + S::OFF_K + ks0 * OT::BYTES, k1_addr = base + S::OFF_K + ks1 * OT::BYTES;
           if (!(ok = chunk_mma(q_addr, k0_addr) && chunk_mma(q_addr, k1_addr))) break;
           umma_commit(bar_k_empty(ks0));
@@ -231,9 +223,7 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         }
         for (; k < p.nchunks; ++k, ++kit) {
           const int ks = kit % S::KS;
-          WMM_TRACE_T0(t_kf);
           if (!(ok = mbar_wait(bar_k_full(ks), (kit / S::KS) & 1, abort_flag))) break;
-          WMM_TRACE_ACC(w_kf, t_kf);
           const uint32_t k_addr = base + S::OFF_K + ks * OT::BYTES;
           if (!(ok = chunk_mma(q_addr, k_addr))) break;
           umma_commit(bar_k_empty(ks));
@@ -241,13 +231,8 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         if (ok) umma_commit(bar_q_empty(qs));
       }
       WMM_TRACE_POINT(6);
-      WMM_TRACE_STORE(23, w_qf);
-      WMM_TRACE_STORE(24, w_kf);
-      WMM_TRACE_STORE(25, w_ae);
-      WMM_TRACE_STORE(28, w_is);
-      WMM_TRACE_STORE(29, w_cm);
     }
-  } else {
+  } else if (warp < 2 + 4 * EPI_GROUPS) {
     // ---------------- epilogue groups: thread <-> band row of the tile ----------------
     // A work item is HALF a chunk: 128 rows x 64 columns = one TMA box of the band.  Items go to the
     // four groups round-robin; both halves of a chunk read the same accumulator stage.
@@ -256,27 +241,23 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     const int rr = quarter * 32 + lane;
     const bool leader = (threadIdx.x == 64 + grp * EPI_THREADS);
     const uint32_t bar_id = 1 + grp;
-    const uint32_t stage0 = base + S::OFF_STAGE + grp * (S::STAGE_BUFS * S::STAGE_HALF);
-    int own = 0;   // items this group has staged so far: picks the staging box
+    int seen = 0;   // items this group has taken so far: picks the verdict word
     const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
     const int W = 2 * p.w + 1;
     const int items_per_tile = 2 * (paired ? p.nchunks - 1 : p.nchunks);
     uint16_t *band = static_cast<uint16_t *>(p.band);
     int cit = 0, iit = 0, rot = 0;  // chunks (accumulator stages) of earlier tiles / half-chunk items seen so far / group rotation
-    unsigned long long w_af = 0, w_st = 0, w_cv = 0, n_items = 0;   // (trace builds) leader: waits, conversion time, items
-    (void)w_af; (void)w_st; (void)w_cv; (void)n_items;
-    int tl = 0;   // (trace builds) own items so far: group 0's leader records a timeline of its first 16 items
-    (void)tl;
-#define NT_TL(k) do { if (leader && grp == 0 && tl < 12) WMM_TRACE_STORE(32 + 10 * tl + (k), (unsigned long long)clock64()); } while (0)
-    int skips = 0; (void)skips;
+    // Items go to the groups round-robin over the CTA's whole item sequence.  When a tile has a multiple of four items,
+    // its first two (the merged ones, the costliest) would always land on groups 0 and 1: the assignment is then
+    // shifted by two from tile to tile.
+    const int rot_step = (items_per_tile % EPI_GROUPS) == 0 ? 2 : 0;
+    int tl = 0;   // tiles of this CTA so far
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
       const int b = tile / p.tiles_per_batch, r0 = (tile % p.tiles_per_batch) * TILE;
       const int i = r0 + rr;
       const int vr = min(TILE, p.M - r0);  // valid rows of this tile
       const bool rows_ok = rr < vr;
-      // Items go to the groups round-robin over the CTA's whole item sequence, shifted by two from tile to tile so that
-      // the merged items (the costly ones, always the first two of a tile) do not always land on the same two groups.
       // A group visits only its own items: the loop body is large, and an iteration that merely skips an item still
       // costs two jumps across it.
       const int tile_iit = iit;   // items of earlier tiles
@@ -286,27 +267,24 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         // stage of this item's chunk: with pairing the tile's stages hold chunks 0, last, 1, 2, ... in this order
         const int a0 = cit + (paired ? (item == 0 ? 0 : item + 1) : item);
         const int as = a0 % ACC_STAGES, as2 = (a0 + 1) % ACC_STAGES;
-        const uint32_t stage = stage0 + (uint32_t)(own % S::STAGE_BUFS) * S::STAGE_HALF;
         const int c = pair_item ? 0 : item;  // chunk index (with pairing, items 1.. are chunks 1..)
-        const bool staged = pair_item || ((c >= 1) && (c * CHUNK + CHUNK - 1 <= 2 * p.w));
-        NT_TL(0);
+        // staged items (boxes wholly inside the band, stored by TMA) are numbered through the CTA's whole sequence
+        const bool staged = hitem >= st_first && hitem < st_first + st_count;
+        const int sidx = tl * st_count + (hitem - st_first);
+        const int sx = sidx % S::STAGE_BOXES;
+        const uint32_t stage = base + S::OFF_STAGE + (uint32_t)sx * S::STAGE_HALF;
+        volatile int *verdict = epi_ok + 2 * grp + (seen & 1);
+        ++seen;
         if (leader) {
-          WMM_TRACE_T0(t_af);
           int good = mbar_wait(bar_acc_full(as), (a0 / ACC_STAGES) & 1, abort_flag) ? 1 : 0;
           if (good && pair_item) good = mbar_wait(bar_acc_full(as2), ((a0 + 1) / ACC_STAGES) & 1, abort_flag) ? 1 : 0;
-          WMM_TRACE_ACC(w_af, t_af);
-          NT_TL(1);
           if (grp == 0 && iit == 0) WMM_TRACE_POINT(7);
-          WMM_TRACE_T0(t_st);
-          if (staged) bulk_wait_read<S::STAGE_BUFS - 1>();  // the store that last used this staging box has drained it
-          WMM_TRACE_ACC(w_st, t_st);
-          NT_TL(2);
-          epi_ok[grp] = good;
+          // the store that last used this staging box has read it
+          if (good && staged) good = mbar_wait(bar_st_free(sx), ((sidx / S::STAGE_BOXES) & 1) ^ 1, abort_flag) ? 1 : 0;
+          *verdict = good;
         }
         named_bar_sync(bar_id, EPI_THREADS);
-        NT_TL(3);
-        WMM_TRACE_T0(t_cv);
-        if (!(ok = (epi_ok[grp] != 0))) break;
+        if (!(ok = (*verdict != 0))) break;
         tc_fence_after_sync();
         const uint32_t taddr = tmem_base + as * CHUNK + h * HALF + lane_sel;  // columns 64*h .. of chunk c
         // positions of chunk c inside the sequence: columns kk in [kk_lo, kk_hi)
@@ -314,25 +292,6 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         const int kk_lo = p.lo - p0, kk_hi = p.hi - p0;
         const bool edge = kk_lo > 0 || kk_hi < CHUNK;
 
-#ifdef WMM_TRACE
-        if (p.dbg & 2) {   // experiment: no conversion at all
-          tc_fence_before_sync();
-          mbar_arrive(bar_acc_empty(as));
-          if (pair_item) mbar_arrive(bar_acc_empty(as2));
-        } else if (pair_item && (p.dbg & 4)) {   // experiment: pair items at the cost of plain ones
-          uint32_t va[32], vb[32];
-          tmem_ld_x32(taddr, va);
-          tmem_ld_x32(taddr + 32, vb);
-          tmem_ld_wait();
-#pragma unroll
-          for (int q4 = 0; q4 < 4; q4++) st_shared_v4(stage_addr(stage, rr, q4), pack8<BF16>(&va[q4 * 8]));
-#pragma unroll
-          for (int q4 = 0; q4 < 4; q4++) st_shared_v4(stage_addr(stage, rr, 4 + q4), pack8<BF16>(&vb[q4 * 8]));
-          tc_fence_before_sync();
-          mbar_arrive(bar_acc_empty(as));
-          mbar_arrive(bar_acc_empty(as2));
-        } else
-#endif
         if (PAIRED && pair_item) {
           // ---- merged first + last chunk ----
           // A warp owns rows 32*quarter .. +31.  Column blocks left of its diagonal block hold only
@@ -426,7 +385,6 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           // the values are in registers: the accumulator half is free for the next chunk before the conversion starts
           tc_fence_before_sync();
           mbar_arrive(bar_acc_empty(as));
-          NT_TL(4);
           if (edge) {
             mask_columns(va, h * 64, kk_lo, kk_hi);
             mask_columns(vb, h * 64 + 32, kk_lo, kk_hi);
@@ -435,7 +393,6 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           for (int q4 = 0; q4 < 4; q4++) st_shared_v4(stage_addr(stage, rr, q4), pack8<BF16>(&va[q4 * 8]));
 #pragma unroll
           for (int q4 = 0; q4 < 4; q4++) st_shared_v4(stage_addr(stage, rr, 4 + q4), pack8<BF16>(&vb[q4 * 8]));
-          NT_TL(5);
         } else if (!PAIRED) {
           // ---- triangular / ragged chunk of an unpaired window: predicated stores from registers.
           // Groups of 8 columns start on 16-byte boundaries of the band tensor, so whole groups go out
@@ -466,41 +423,41 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           mbar_arrive(bar_acc_empty(as));
         }
 
-        if (staged) {
+        if (staged) {   // hand the box to the store issuer
           fence_proxy_async_smem();
-          named_bar_sync(bar_id, EPI_THREADS);
-          NT_TL(6);
-          if (leader) {
-            WMM_TRACE_ACC(w_cv, t_cv);
-            ++n_items;
-#ifdef WMM_TRACE
-            if (!(p.dbg & 1))
-#endif
-            {
-              tma_store_3d(&map_band, stage, r0 + c * CHUNK + h * 64, r0, b);  // x = i + j of the box's first column
-              bulk_commit();
-            }
-            if (grp == 0 && iit == 0) WMM_TRACE_POINT(8);
-          }
+          mbar_arrive(bar_st_full(sx));
         }
-        if (staged) ++own;
-        NT_TL(7);
-        ++tl;
-        skips = 0;
       }
       cit += p.nchunks;
       iit += items_per_tile;
-      rot += 2;
+      rot += rot_step;
+      ++tl;
     }
     if (leader && grp == 0) WMM_TRACE_POINT(9);
-    if (leader && (grp == 0 || grp == 2)) {
-      WMM_TRACE_STORE(13 + 2 * grp, w_af);
-      WMM_TRACE_STORE(14 + 2 * grp, w_st);
-      WMM_TRACE_STORE(15 + 2 * grp, w_cv);
-      WMM_TRACE_STORE(16 + 2 * grp, n_items);
+  } else {
+    // ---------------- store issuer: every staged item of the CTA, in item order ----------------
+    if (lane == 0) {
+      int sidx = 0;   // staged items so far
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
+        const int b = tile / p.tiles_per_batch, r0 = (tile % p.tiles_per_batch) * TILE;
+        for (int k = 0; k < st_count; ++k, ++sidx) {
+          const int hitem = st_first + k;
+          const int c = (paired && hitem < 2) ? 0 : (hitem >> 1), h = hitem & 1;
+          const int sx = sidx % S::STAGE_BOXES;
+          if (!(ok = mbar_wait(bar_st_full(sx), (sidx / S::STAGE_BOXES) & 1, abort_flag))) break;
+          tma_store_3d(&map_band, base + S::OFF_STAGE + (uint32_t)sx * S::STAGE_HALF, r0 + c * CHUNK + h * 64, r0, b);  // x = i + j of the box's first column
+          bulk_commit();
+          if (sidx == 0) WMM_TRACE_POINT(8);
+          if (sidx >= S::STORE_DEPTH) {
+            bulk_wait_read<S::STORE_DEPTH>();   // all but the newest STORE_DEPTH stores have read their boxes
+            mbar_arrive(bar_st_free((sidx - S::STORE_DEPTH) % S::STAGE_BOXES));
+          }
+        }
+      }
+      bulk_wait_all();
+      WMM_TRACE_POINT(10);
     }
-    if (leader) bulk_wait_all();
-    if (leader && grp == 0) WMM_TRACE_POINT(10);
   }
 
   // ---------------- teardown ----------------
