@@ -17,9 +17,10 @@
 // Per box the SM takes in 32 KB of band + 16 KB of K^T rows (+ 16 KB of Q rows per row tile), against two full
 // passes (2 x 48 KB per box) of the two-pass kernel.
 //
-// Warps: 0 = TMA producer, 1 = MMA issuer / TMEM owner, 2-5 = mask, 6-9 = epilogue.  Waits are bounded as everywhere.
+// Warps: 0 = TMA producer, 1 = MMA issuer of the row products / TMEM owner, 2-5 = mask, 6-9 = epilogue, 10 = MMA issuer of
+// the column products.  Waits are bounded as everywhere.
 
-constexpr int SWP_THREADS = 320;
+constexpr int SWP_THREADS = 352;
 constexpr uint32_t SWP_EPI_BAR = 6;
 constexpr unsigned long long ST_SWEEP_TIMEOUT = 1ull << 4;
 
@@ -116,7 +117,7 @@ band_bwd_sweep_kernel(const __grid_constant__ CUtensorMap map_band, const __grid
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::STAGES; s++) {
       mbar_init(bar_full(s), 1);
-      mbar_init(bar_empty(s), 1);
+      mbar_init(bar_empty(s), 2);   // both MMA issuers
       mbar_init(bar_masked(s), 128);
     }
     for (int s = 0; s < 2; s++) {
@@ -200,9 +201,14 @@ band_bwd_sweep_kernel(const __grid_constant__ CUtensorMap map_band, const __grid
           },
           [&](int, int) { return true; }, [&](int, int) { return true; }, [&](bool) { return true; });
     }
-  } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
+  } else if (warp == 1 || warp == 10) {
+    // ---------------- MMA issuers ----------------
+    // Two threads issue the MMAs, each walking all boxes: warp 1 the row products (grad_Q = box . K^T rows, into the
+    // row accumulators), warp 10 the column products (grad_K^T = box^T . Q rows, into the column slots).  Issuing an
+    // MMA costs its thread about as much as the tensor core needs to execute it, and a box feeds sixteen of them: one
+    // thread alone was busy three quarters of the kernel's time.  A stage is released when both have committed.
     if (lane == 0) {
+      const bool rows = warp == 1;
       constexpr uint32_t IDESC_N = instr_desc_f16(BF16, false, true, TILE, NH);
       constexpr uint32_t IDESC_T = instr_desc_f16(BF16, true, true, TILE, NH);
       constexpr uint64_t ADESC_N = BT::DESC;
@@ -213,17 +219,20 @@ band_bwd_sweep_kernel(const __grid_constant__ CUtensorMap map_band, const __grid
       int as = 0, xb = 0;
       unsigned long long w_wait = 0, w_issue = 0;   // (trace builds) time in waits / issuing MMAs and commits
       (void)w_wait; (void)w_issue;
-      WMM_TRACE_POINT(1);
+      WMM_TRACE_POINT(rows ? 1 : 5);
       sweep_walk(
           p,
           [&](int, int, bool warm) {
-            xb = xrow & 1;
-            if (!mbar_wait(bar_xfull(xb), (xrow >> 1) & 1, abort_flag)) return false;
-            ++xrow;
-            if (!warm) {
-              as = nrow & 1;
-              if (!mbar_wait(bar_nempty(as), ((nrow >> 1) & 1) ^ 1, abort_flag)) return false;
-              ++nrow;
+            if (rows) {
+              if (!warm) {
+                as = nrow & 1;
+                if (!mbar_wait(bar_nempty(as), ((nrow >> 1) & 1) ^ 1, abort_flag)) return false;
+                ++nrow;
+              }
+            } else {
+              xb = xrow & 1;
+              if (!mbar_wait(bar_xfull(xb), (xrow >> 1) & 1, abort_flag)) return false;
+              ++xrow;
             }
             return true;
           },
@@ -238,7 +247,7 @@ band_bwd_sweep_kernel(const __grid_constant__ CUtensorMap map_band, const __grid
             ++it;
             const int slot = pt % nslots;
             const bool col_first = t_pass && r == max(pt - p.D, 0);
-            if (col_first) {  // a new column starts in this slot: the previous one must have been drained
+            if (!rows && col_first) {  // a new column starts in this slot: the previous one must have been drained
               if (!mbar_wait(bar_tempty(slot), ((col_bits >> slot) & 1u) ^ 1u, abort_flag)) return false;
               col_bits ^= 1u << slot;
             }
@@ -247,37 +256,37 @@ band_bwd_sweep_kernel(const __grid_constant__ CUtensorMap map_band, const __grid
             tc_fence_after_sync();
             const uint32_t a_addr = base + s * S::STAGE_BYTES, y_addr = a_addr + BT::BYTES;
             const uint32_t x_addr = base + S::OFF_X + xb * OT::BYTES;
-            if (!warm) {
+            if (rows && !warm) {
 #pragma unroll
               for (int k = 0; k < 8; k++)
                 umma_f16(tmem_row(as), smem_desc(ADESC_N, a_addr + BT::kstep_offset(k)),
                          smem_desc(BDESC, y_addr + (uint32_t)k * 16u * OT::SW_BYTES), IDESC_N, (!first_in_row || k > 0) ? 1u : 0u);
             }
-            if (t_pass) {
+            if (!rows && t_pass) {
 #pragma unroll
               for (int k = 0; k < 8; k++)
                 umma_f16(tmem_col(slot), smem_desc(ADESC_T, a_addr + (uint32_t)k * 2048u),
                          smem_desc(BDESC, x_addr + (uint32_t)k * 16u * OT::SW_BYTES), IDESC_T, (!col_first || k > 0) ? 1u : 0u);
             }
-            umma_commit(bar_empty(s));
+            umma_commit(bar_empty(s));   // (arrives at once when this thread issued nothing from the stage)
             WMM_TRACE_ACC(w_issue, t_i);
             return true;
           },
           [&](int, int pt) {
-            umma_commit(bar_tfull(pt % nslots));
+            if (!rows) umma_commit(bar_tfull(pt % nslots));
             return true;
           },
           [&](int, int) {
-            umma_commit(bar_nfull(as));
+            if (rows) umma_commit(bar_nfull(as));
             return true;
           },
           [&](bool) {
-            umma_commit(bar_xempty(xb));
+            if (!rows) umma_commit(bar_xempty(xb));
             return true;
           });
-      WMM_TRACE_POINT(2);
-      WMM_TRACE_STORE(3, w_wait);
-      WMM_TRACE_STORE(4, w_issue);
+      WMM_TRACE_POINT(rows ? 2 : 6);
+      WMM_TRACE_STORE(rows ? 3 : 7, w_wait);
+      WMM_TRACE_STORE(rows ? 4 : 8, w_issue);
     }
   } else if (warp < 6) {
     // ---------------- mask warps: thread <-> row of the band box ----------------
