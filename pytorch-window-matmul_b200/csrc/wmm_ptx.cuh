@@ -44,6 +44,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Wall-clock bound of any single wait.  Kernels of this library run for microseconds to milliseconds.
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;
 
+#ifdef WMM_TRACE
+// (trace builds) the first wait of a kernel that ran out: barrier address, parity, block, thread
+static __device__ unsigned long long g_wait_info[4] = {0, 0, 0, 0};
+// ... and, for every warp of every block that abandoned a wait: (barrier address << 8) | (parity << 4) | 1
+static __device__ unsigned long long g_wait_tab[160 * 20];
+#endif
+
 // Waits for the phase with the given parity to complete.  Returns false if the wait was abandoned,
 // either because it ran out (then *abort_flag is set) or because another role of the CTA set the flag.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
@@ -54,6 +61,39 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 #ifdef WMM_SPIN_SLEEP
     __nanosleep(WMM_SPIN_SLEEP);
 #endif
+    if ((spin & 63u) == 0u) {
+#ifdef WMM_TRACE
+      if (*abort_flag) {
+        if (blockIdx.x < 160 && (threadIdx.x >> 5) < 20)
+          g_wait_tab[blockIdx.x * 20 + (threadIdx.x >> 5)] = ((unsigned long long)bar << 8) | (parity << 4) | 1ull;
+        return false;
+      }
+#endif
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+#ifdef WMM_TRACE
+        if (atomicCAS(&g_wait_info[0], 0ull, (unsigned long long)bar + 1ull) == 0ull) {
+          g_wait_info[1] = parity;
+          g_wait_info[2] = blockIdx.x;
+          g_wait_info[3] = threadIdx.x;
+        }
+        if (blockIdx.x < 160 && (threadIdx.x >> 5) < 20)
+          g_wait_tab[blockIdx.x * 20 + (threadIdx.x >> 5)] = ((unsigned long long)bar << 8) | (parity << 4) | 3ull;
+#endif
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+
+// Waits until a counter in shared memory that another thread of the CTA only ever increases has reached `want`.  Bounded
+// like mbar_wait.  The caller orders its later accesses behind the wait with a CTA barrier.
+__device__ __forceinline__ bool count_wait(volatile int *counter, int want, volatile int *abort_flag) {
+  if (*counter >= want) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (uint32_t spin = 1;; ++spin) {
+    if (*counter >= want) return true;
     if ((spin & 63u) == 0u) {
       if (*abort_flag) return false;
       if (globaltimer_ns() - t0 > kWaitLimitNs) {

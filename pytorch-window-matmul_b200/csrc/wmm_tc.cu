@@ -57,9 +57,24 @@ __device__ unsigned long long g_trace[160 * kTraceSlots];
   do {                                                                              \
     if (blockIdx.x < 160) g_trace[blockIdx.x * kTraceSlots + (id)] = (value);       \
   } while (0)
+extern "C" __attribute__((visibility("default"))) int wmm_trace_waits(unsigned long long *out, int clear) {
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out, ptx::g_wait_tab, sizeof(ptx::g_wait_tab));
+  if (e == cudaSuccess && clear) {
+    void *p = nullptr;
+    e = cudaGetSymbolAddress(&p, ptx::g_wait_tab);
+    if (e == cudaSuccess) e = cudaMemset(p, 0, sizeof(ptx::g_wait_tab));
+  }
+  return e == cudaSuccess ? 160 * 20 : -1;
+}
 extern "C" __attribute__((visibility("default"))) int wmm_trace_read(unsigned long long *out, int clear) {
   cudaError_t e = cudaDeviceSynchronize();
   if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace));
+  if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out + 159 * kTraceSlots, ptx::g_wait_info, sizeof(ptx::g_wait_info));   // (block 159 never exists)
+  if (e == cudaSuccess && clear) {
+    const unsigned long long zero[4] = {0, 0, 0, 0};
+    e = cudaMemcpyToSymbol(ptx::g_wait_info, zero, sizeof(zero));
+  }
   if (e == cudaSuccess && clear) {
     void *p = nullptr;
     e = cudaGetSymbolAddress(&p, g_trace);
@@ -192,7 +207,8 @@ cudaError_t launch_pdl(void (*kern)(KArgs...), int grid, int block, size_t smem,
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  static const bool no_pdl = getenv("WMM_NO_PDL") != nullptr;
+  cfg.numAttrs = no_pdl ? 0 : 1;
   return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
 }
 

@@ -48,7 +48,7 @@ template <int NH> struct NtSmem {
   static constexpr int OFF_K = OFF_Q + QS * OT::BYTES;
   static constexpr int OFF_STAGE = OFF_K + KS * OT::BYTES;  // STAGE_BOXES boxes of 16 KB
   static constexpr int OFF_BARS = OFF_STAGE + STAGE_BOXES * STAGE_HALF;
-  static constexpr int NBARS = 2 * QS + 2 * KS + 2 * ACC_STAGES + 2 * STAGE_BOXES;
+  static constexpr int NBARS = 2 * QS + 2 * KS + 2 * ACC_STAGES + STAGE_BOXES;
   static constexpr int OFF_MISC = OFF_BARS + NBARS * 8;
   static constexpr int BYTES = OFF_MISC + 64;
   static constexpr int ALLOC = BYTES + 1024;  // slack to align the base to 1024 B
@@ -101,9 +101,14 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   auto bar_k_empty = [&](int s) { return bars + 8u * (2 * S::QS + S::KS + s); };
   auto bar_acc_full = [&](int s) { return bars + 8u * (2 * S::QS + 2 * S::KS + s); };
   auto bar_acc_empty = [&](int s) { return bars + 8u * (2 * S::QS + 2 * S::KS + ACC_STAGES + s); };
-  // staging box x: filled by an epilogue group (all its threads arrive), handed back by the store issuer
+  // staging box x has been filled by an epilogue group (all its threads arrive)
   auto bar_st_full = [&](int x) { return bars + 8u * (2 * S::QS + 2 * S::KS + 2 * ACC_STAGES + x); };
-  auto bar_st_free = [&](int x) { return bars + 8u * (2 * S::QS + 2 * S::KS + 2 * ACC_STAGES + S::STAGE_BOXES + x); };
+  // Boxes come back in item order, so one counter says which are free again: the number of staged items whose store has
+  // read its box.  Item n may fill box n % STAGE_BOXES once item n - STAGE_BOXES is among them.  (A counter, not an
+  // mbarrier per box: a group may reach its wait for a box before the group of the box's previous item has reached its
+  // own, and a parity wait cannot tell the phase it wants from the one two earlier.  Accumulator stages cannot be
+  // overtaken like that: a stage is refilled only after both groups of its previous chunk have read it.)
+  volatile int *st_freed = reinterpret_cast<volatile int *>(base_ptr + S::OFF_MISC + 48);
   volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + S::OFF_MISC);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(base_ptr + S::OFF_MISC + 4);
   volatile int *epi_ok = reinterpret_cast<volatile int *>(base_ptr + S::OFF_MISC + 8);  // two per group, used in turn
@@ -125,7 +130,8 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     for (int s = 0; s < S::QS; s++) { mbar_init(bar_q_full(s), 1); mbar_init(bar_q_empty(s), 1); }
     for (int s = 0; s < S::KS; s++) { mbar_init(bar_k_full(s), 1); mbar_init(bar_k_empty(s), 1); }
     for (int s = 0; s < ACC_STAGES; s++) { mbar_init(bar_acc_full(s), 1); mbar_init(bar_acc_empty(s), 2 * EPI_THREADS); }
-    for (int x = 0; x < S::STAGE_BOXES; x++) { mbar_init(bar_st_full(x), EPI_THREADS); mbar_init(bar_st_free(x), 1); }
+    for (int x = 0; x < S::STAGE_BOXES; x++) mbar_init(bar_st_full(x), EPI_THREADS);
+    *st_freed = 0;
     *abort_flag = 0;
     for (int g = 0; g < 2 * EPI_GROUPS; g++) epi_ok[g] = 1;
     fence_mbar_init();
@@ -280,7 +286,7 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           if (good && pair_item) good = mbar_wait(bar_acc_full(as2), ((a0 + 1) / ACC_STAGES) & 1, abort_flag) ? 1 : 0;
           if (grp == 0 && iit == 0) WMM_TRACE_POINT(7);
           // the store that last used this staging box has read it
-          if (good && staged) good = mbar_wait(bar_st_free(sx), ((sidx / S::STAGE_BOXES) & 1) ^ 1, abort_flag) ? 1 : 0;
+          if (good && staged) good = count_wait(st_freed, sidx - S::STAGE_BOXES + 1, abort_flag) ? 1 : 0;
           *verdict = good;
         }
         named_bar_sync(bar_id, EPI_THREADS);
@@ -451,7 +457,7 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           if (sidx == 0) WMM_TRACE_POINT(8);
           if (sidx >= S::STORE_DEPTH) {
             bulk_wait_read<S::STORE_DEPTH>();   // all but the newest STORE_DEPTH stores have read their boxes
-            mbar_arrive(bar_st_free((sidx - S::STORE_DEPTH) % S::STAGE_BOXES));
+            *st_freed = sidx - S::STORE_DEPTH + 1;
           }
         }
       }
