@@ -300,6 +300,8 @@ def run_ours(args, torch):
     B, M, N, w, dt, distn = WORKLOADS[args.workload]
     dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[dt]
     e = 2 if dt != "fp32" else 4
+    if args.tf32:
+        impl.set_flags(N_.FLAG_TF32)
     if args.shard == "seq" or (args.shard == "auto" and args.workload == "c4" and world > 1):
         return run_seq_sharded(args, torch, impl, N_, rank, world, dev)
     # strong scaling: the same B sequences, split evenly over the ranks (the last rank may get fewer)
@@ -588,6 +590,7 @@ def run_ours(args, torch):
                 "l2": "no flush: one step touches %.0f MB per GPU, larger than the 126 MB L2" % (total_bytes / world / 1e6),
                 "launch": ("cuda graph of %d kernels, %s" % (launches_per_step, "dependency DAG" if args.branches == 2 else "one chain")) if graph is not None else "%d stream launches" % launches_per_step,
                 "k_layout": "contiguous (B,N,M)" if args.k_layout == "bnm" else "transposed view of (B,M,N)",
+                **({"fp32_mode": "tf32 products on the tensor cores (WMM_FLAG_TF32)" if args.tf32 else "exact-order fp32"} if dt == "fp32" else {}),
             },
             "step_roofline": {
                 "alg_MB": round(total_bytes / 1e6, 1), "alg_GFLOP": round(total_flops / 1e9, 1),
@@ -897,6 +900,7 @@ def main():
     ap.add_argument("--blocks", type=int, default=0, help="timed blocks of --steps steps each (0: enough for about a second, at least 50)")
     ap.add_argument("--no-reference-cuda", action="store_true", help="skip the short run of the reference's CUDA kernels beside the headline")
     ap.add_argument("--no-seq-extra", action="store_true", help="on several GPUs: skip the sequence-sharded config 4 step reported beside the headline")
+    ap.add_argument("--tf32", action="store_true", help="fp32 workloads: multiply on the tensor cores as tf32 (WMM_FLAG_TF32) instead of the exact-order kernels")
     ap.add_argument("--branches", type=int, default=2, choices=[1, 2], help="capture the step as one chain (1) or with its real dependencies (2)")
     ap.add_argument("--no-graph", action="store_true", help="launch the six kernels on the stream instead of a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -85,7 +85,12 @@ enum {
   /* wmm_window_bwd only: take the one-sweep kernel (each box of grad_A staged once for both products) whenever the
    * shape allows it, also for small problems where the library would choose the two-pass kernel because the boxes a
    * CTA replays at the start of its run outweigh the saving (testing the kernel on small cases). */
-  WMM_FLAG_PREFER_SWEEP = 1u << 4
+  WMM_FLAG_PREFER_SWEEP = 1u << 4,
+  /* WMM_F32 only: multiply on the tensor cores with the operands rounded to tf32 (10-bit mantissa) and fp32 sums,
+   * wherever a tensor-core kernel takes the problem (wmm_query_path says which); results are then within about 2e-3
+   * relative of the exact fp32 result instead of 1e-5.  Without the flag fp32 always takes the exact-order kernels.
+   * The reference has one fp32 path (window_matmul_cuda.cu:257, AT_DISPATCH_FLOATING_TYPES_AND_HALF), exact. */
+  WMM_FLAG_TF32 = 1u << 5
 };
 
 /* A (batch, rows, cols) operand addressed by ELEMENT strides: either of the two inner strides may be

@@ -109,22 +109,24 @@ constexpr int CHUNK = 128;      // positions per chunk = MMA N of band_nt
 constexpr int ACC_STAGES = 4;   // band_nt: 4 x 128 TMEM columns (one chunk each)
 // Status codes OR-ed into g_device_status when a bounded wait runs out: bit 0 band_nt, bit 1 band_n / band_t.
 
-// A (128 rows x NH) 16-bit operand tile in shared memory, K-major, written by TMA with the hardware
-// swizzle and read by tcgen05.mma through a matching descriptor.  Rows are SW_BYTES long; wider tiles
-// are split into boxes of 64 columns.
-template <int NH> struct KMajorTile {
-  static constexpr int BOXK = NH >= 64 ? 64 : NH;
-  static constexpr int SW_BYTES = BOXK * 2;
+// A (128 rows x NH) operand tile in shared memory, K-major, written by TMA with the hardware swizzle and read by
+// tcgen05.mma through a matching descriptor.  ES = bytes per element (2: fp16 / bf16, 4: fp32 consumed as tf32).  Rows are
+// SW_BYTES long; wider tiles are split into boxes of 128 bytes.  One k-step of the MMA is 32 bytes of a row (16 or 8
+// elements) whatever the type.
+template <int NH, int ES> struct KMajorTileE {
+  static constexpr int BOXK = (NH * ES >= 128) ? 128 / ES : NH;
+  static constexpr int SW_BYTES = BOXK * ES;
   static constexpr int NBOX = NH / BOXK;
   static constexpr int BOX_BYTES = 128 * SW_BYTES;
   static constexpr int BYTES = NBOX * BOX_BYTES;
   static constexpr uint32_t SWZ_CODE = SW_BYTES == 128 ? 2u : SW_BYTES == 64 ? 4u : 6u;
-  static constexpr int KSTEPS = NH / 16;
+  static constexpr int KSTEPS = NH * ES / 32;
   static constexpr uint64_t DESC = smem_desc_base(16, 8 * SW_BYTES, SWZ_CODE);
   static __device__ __forceinline__ uint32_t kstep_offset(int ks) {
-    return (uint32_t)((ks * 16 / BOXK) * BOX_BYTES + (ks * 16 % BOXK) * 2);
+    return (uint32_t)((ks * 32 / SW_BYTES) * BOX_BYTES + (ks * 32 % SW_BYTES));
   }
 };
+template <int NH> using KMajorTile = KMajorTileE<NH, 2>;
 
 template <bool BF16> __device__ __forceinline__ uint32_t pack2(uint32_t lo_bits, uint32_t hi_bits) {
   const float lo = __uint_as_float(lo_bits), hi = __uint_as_float(hi_bits);
@@ -151,6 +153,7 @@ template <bool BF16> __device__ __forceinline__ uint16_t pack1(uint32_t bits) {
 
 #include "wmm_tc_mm.cuh"
 #include "wmm_tc_sweep.cuh"
+#include "wmm_tc_mm32.cuh"
 
 // ---------------------------------------------------------------------------------------------------
 // host side
@@ -219,15 +222,21 @@ CUtensorMapSwizzle swizzle_for(int bytes) {
 }
 
 // 3-D map (columns, rows, batch) over a 16-bit operand with unit column stride; box = (boxk x 128 x 1).
-bool make_operand_map(CUtensorMap *m, bool bf16, const void *data, int cols, int rows, int batch, int64_t stride_r,
-                      int64_t stride_b, int boxk) {
+// `et`: 0 fp16, 1 bf16 (bool true), 2 fp32.
+CUtensorMapDataType map_dtype(int et) {
+  return et == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : et == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+}
+bool make_operand_map(CUtensorMap *m, int et, const void *data, int cols, int rows, int batch, int64_t stride_r,
+                      int64_t stride_b, int boxk, int box_rows = 128, bool atom32 = false) {
+  const int es = et == 2 ? 4 : 2;
   const cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};
-  const cuuint64_t strides[2] = {(cuuint64_t)stride_r * 2, (cuuint64_t)(batch > 1 ? stride_b : (int64_t)rows * stride_r) * 2};
-  const cuuint32_t box[3] = {(cuuint32_t)boxk, 128, 1};
+  const cuuint64_t strides[2] = {(cuuint64_t)stride_r * es, (cuuint64_t)(batch > 1 ? stride_b : (int64_t)rows * stride_r) * es};
+  const cuuint32_t box[3] = {(cuuint32_t)boxk, (cuuint32_t)box_rows, 1};
   const cuuint32_t estr[3] = {1, 1, 1};
-  const CUresult r = encode_fn()(m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+  const CUresult r = encode_fn()(m, map_dtype(et), 3,
                                 const_cast<void *>(data), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                swizzle_for(boxk * 2), CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                                atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : swizzle_for(boxk * es), CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     set_launch_detail("cuTensorMapEncodeTiled(operand %p, dims %d x %d x %d, strides %lld / %lld elements) returned %d", data, cols,
                       rows, batch, (long long)stride_r, (long long)stride_b, (int)r);
@@ -254,14 +263,15 @@ bool make_operand_map_mn(CUtensorMap *m, bool bf16, const void *data, int cols, 
 // The band as a pitched matrix: x = i + j in [0, M + 2w), row i with pitch 2w elements, batch with
 // pitch M*(2w+1).  Rows overlap in memory by design (pitch < extent); an in-range (x, i, b) never
 // addresses memory outside the tensor.  Box = (64 x 128 x 1), 128-byte swizzle.
-bool make_band_map(CUtensorMap *m, bool bf16, const void *band, int M, int w, int batch) {
+bool make_band_map(CUtensorMap *m, int et, const void *band, int M, int w, int batch, int box_rows = 128, bool atom32 = false) {
+  const int es = et == 2 ? 4 : 2;
   const cuuint64_t dims[3] = {(cuuint64_t)M + 2ull * w, (cuuint64_t)M, (cuuint64_t)batch};
-  const cuuint64_t strides[2] = {(cuuint64_t)(2 * w) * 2, (cuuint64_t)M * (2ull * w + 1) * 2};
-  const cuuint32_t box[3] = {64, 128, 1};
+  const cuuint64_t strides[2] = {(cuuint64_t)(2 * w) * es, (cuuint64_t)M * (2ull * w + 1) * es};
+  const cuuint32_t box[3] = {(cuuint32_t)(128 / es), (cuuint32_t)box_rows, 1};   // 128-byte lines
   const cuuint32_t estr[3] = {1, 1, 1};
-  const CUresult r = encode_fn()(m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+  const CUresult r = encode_fn()(m, map_dtype(et), 3,
                                 const_cast<void *>(band), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                                atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     set_launch_detail("cuTensorMapEncodeTiled(band %p, rows %d, window %d, batch %d) returned %d", band, M, w, batch, (int)r);
   return r == CUDA_SUCCESS;
@@ -285,9 +295,10 @@ bool y_position_major(const Problem &p) {
 
 bool band_tma_ok(const void *band, int M, int w) { return aligned16(band) && (w % 4) == 0 && w >= 4 && (M % 8) == 0; }
 
-template <bool BF16, int NH, bool YMN, bool PAIRED> cudaError_t launch_nt(const Problem &p, cudaStream_t stream) {
-  using S = NtSmem<NH>;
-  using OT = KMajorTile<NH>;
+template <int ET, int NH, bool YMN, bool PAIRED> cudaError_t launch_nt(const Problem &p, cudaStream_t stream) {
+  constexpr int BF16 = ET;   // (element type code of the tensor maps)
+  using S = NtSmem<NH, ET == 2 ? 4 : 2>;
+  using OT = KMajorTileE<NH, ET == 2 ? 4 : 2>;
   NtParams k;
   k.B = p.B; k.M = p.M; k.w = p.w; k.off = p.off; k.lo = p.lo; k.hi = p.hi;
   k.tiles_per_batch = (p.M + TILE - 1) / TILE;
@@ -295,7 +306,7 @@ template <bool BF16, int NH, bool YMN, bool PAIRED> cudaError_t launch_nt(const 
   k.nchunks = (TILE + 2 * p.w + CHUNK - 1) / CHUNK;
   k.paired = PAIRED ? 1 : 0;
   k.band = p.o;
-  auto kern = band_nt_tc_kernel<BF16, NH, YMN, PAIRED>;
+  auto kern = band_nt_tc_kernel<ET, NH, YMN, PAIRED>;
   // the attribute is per device; setting it on every call is cheap and needs no per-device cache
   cudaError_t attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::ALLOC);
   if (attr_err != cudaSuccess) {
@@ -316,14 +327,18 @@ template <bool BF16, int NH, bool YMN, bool PAIRED> cudaError_t launch_nt(const 
 }
 
 template <int NH> cudaError_t launch_nt_any(const Problem &p, cudaStream_t stream) {
+  if (p.dtype == WMM_F32) {   // tf32 products, fp32 band
+    if constexpr (NH <= 64) return launch_nt<2, NH, false, false>(p, stream);
+    else return cudaErrorNotSupported;
+  }
   const bool bf16 = p.dtype == WMM_BF16;
   const bool paired = (p.w % 64) == 0;   // 2w a multiple of 128
   if (y_position_major(p)) {
-    if (paired) return bf16 ? launch_nt<true, NH, true, true>(p, stream) : launch_nt<false, NH, true, true>(p, stream);
-    return bf16 ? launch_nt<true, NH, true, false>(p, stream) : launch_nt<false, NH, true, false>(p, stream);
+    if (paired) return bf16 ? launch_nt<1, NH, true, true>(p, stream) : launch_nt<0, NH, true, true>(p, stream);
+    return bf16 ? launch_nt<1, NH, true, false>(p, stream) : launch_nt<0, NH, true, false>(p, stream);
   }
-  if (paired) return bf16 ? launch_nt<true, NH, false, true>(p, stream) : launch_nt<false, NH, false, true>(p, stream);
-  return bf16 ? launch_nt<true, NH, false, false>(p, stream) : launch_nt<false, NH, false, false>(p, stream);
+  if (paired) return bf16 ? launch_nt<1, NH, false, true>(p, stream) : launch_nt<0, NH, false, true>(p, stream);
+  return bf16 ? launch_nt<1, NH, false, false>(p, stream) : launch_nt<0, NH, false, false>(p, stream);
 }
 
 // MODE 0 / 1: one problem (band_n / band_t).  MODE 2: `p` is the band_n problem and `pt` the band_t
@@ -377,6 +392,33 @@ template <int MODE, bool YMN> cudaError_t launch_mm_n(const Problem &p, const Pr
   }
 }
 
+// fp32 tensors, tf32 products (WMM_FLAG_TF32): band_n (TR = false) or band_t (TR = true)
+template <int NH, bool TR> cudaError_t launch_mm32(const Problem &p, cudaStream_t stream) {
+  using S = Mm32Smem<NH>;
+  const int out_rows = TR ? p.Mo : p.M;
+  const int other_rows = TR ? p.M : p.Mo;
+  MmParams k;
+  k.B = p.B; k.M = p.M; k.Mo = p.Mo; k.w = p.w; k.off = p.off; k.lo = p.lo; k.hi = p.hi;
+  k.tiles_per_batch = (out_rows + TILE - 1) / TILE;
+  k.total_tiles = k.tiles_per_batch * p.B;
+  k.nchunks = (TILE + 2 * p.w + M32_RC - 1) / M32_RC;
+  auto kern = band_mm_tf32_kernel<NH, TR>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::ALLOC);
+  if (e != cudaSuccess) {
+    set_launch_detail("cudaFuncSetAttribute(band_mm tf32, %d bytes of shared memory)", S::ALLOC);
+    return e;
+  }
+  CUtensorMap mband, mother, mout;
+  // MN-major fp32 operands (the other operand; the band box of band_t) use the 128-byte swizzle with 32-byte atoms
+  if (!make_band_map(&mband, 2, p.a, p.M, p.w, p.B, TR ? M32_RC : 128, TR) ||
+      !make_operand_map(&mother, 2, p.b, NH, other_rows, p.B, p.b_sr, p.b_sb, 32, M32_RC, true) ||
+      !make_operand_map(&mout, 2, p.o, NH, out_rows, p.B, p.o_sr, p.o_sb, 32, 128))
+    return cudaErrorInvalidValue;
+  const int grid = persistent_grid(k.total_tiles);
+  set_launch_detail("band_mm tf32 launch, grid %d", grid);
+  return launch_pdl(kern, grid, MM_THREADS, S::ALLOC, stream, mband, mother, mout, k);
+}
+
 // band_n's other operand may be position-major (MODE 0 and the band_n half of MODE 2); band_t's never is here
 template <int MODE> cudaError_t launch_mm_any(const Problem &p, const Problem *pt, cudaStream_t stream) {
   if (MODE != 1 && y_position_major(p)) return launch_mm_n<MODE, true>(p, pt, stream);
@@ -423,6 +465,22 @@ template <bool BF16, int NH> cudaError_t launch_sweep(const Problem &pn, const P
 }  // namespace
 
 bool tensor_eligible(Primitive prim, const Problem &p) {
+  if (p.dtype == WMM_F32) {
+    // fp32 operands go to the tensor cores only on request (WMM_FLAG_TF32: products of tf32-rounded values, fp32 sums)
+    if (!(p.flags & WMM_FLAG_TF32) || !encode_fn()) return false;
+    if (p.N != 32 && p.N != 64) return false;
+    if ((int64_t)p.B * ((p.M + TILE - 1) / TILE) > 0x7fffffffLL) return false;
+    // element strides of fp32 operands: multiples of 4 would do; the 16-bit rule (multiples of 8) is kept
+    if (prim == BAND_NT)
+      return band_tma_ok(p.o, p.M, p.w) && operand_tma_ok(p.a, p.a_sb, p.a_sr, p.a_sc, p.B) &&
+             operand_tma_ok(p.b, p.b_sb, p.b_sr, p.b_sc, p.B) && p.Mo > 0;
+    if (prim == BAND_N)
+      return band_tma_ok(p.a, p.M, p.w) && operand_tma_ok(p.b, p.b_sb, p.b_sr, p.b_sc, p.B) &&
+             operand_tma_ok(p.o, p.o_sb, p.o_sr, p.o_sc, p.B) && p.Mo > 0;
+    // band_t: the box of a tile starts at x = t0 - off + w, a multiple of 4 elements (16 bytes)
+    return band_tma_ok(p.a, p.M, p.w) && ((p.w - p.off) % 4) == 0 && operand_tma_ok(p.b, p.b_sb, p.b_sr, p.b_sc, p.B) &&
+           operand_tma_ok(p.o, p.o_sb, p.o_sr, p.o_sc, p.B) && p.M > 0;
+  }
   if (p.dtype != WMM_F16 && p.dtype != WMM_BF16) return false;
   if (!encode_fn()) return false;
   if (p.N != 32 && p.N != 64 && p.N != 128) return false;
@@ -452,6 +510,10 @@ cudaError_t launch_tensor(Primitive prim, const Problem &p, cudaStream_t stream,
       case 128: e = launch_nt_any<128>(p, stream); break;
     }
   }
+  else if (p.dtype == WMM_F32) {
+    if (prim == BAND_N) e = p.N == 32 ? launch_mm32<32, false>(p, stream) : launch_mm32<64, false>(p, stream);
+    else if (prim == BAND_T) e = p.N == 32 ? launch_mm32<32, true>(p, stream) : launch_mm32<64, true>(p, stream);
+  }
   else if (prim == BAND_N)
     e = launch_mm_any<0>(p, nullptr, stream);
   else if (prim == BAND_T)
@@ -461,6 +523,7 @@ cudaError_t launch_tensor(Primitive prim, const Problem &p, cudaStream_t stream,
 }
 
 bool tensor_fused_pair_eligible(const Problem &pn, const Problem &pt) {
+  if (pn.dtype == WMM_F32) return false;   // fp32 (tf32 products): the two single-product kernels
   return tensor_eligible(BAND_N, pn) && tensor_eligible(BAND_T, pt) && pn.a == pt.a && pn.Mo == pn.M && pt.Mo == pt.M &&
          pn.off == 0 && pt.off == 0 && pn.lo == pt.lo && pn.hi == pt.hi && pn.w == pt.w && pn.N == pt.N && pn.B == pt.B &&
          pn.M == pt.M && pn.dtype == pt.dtype && (int64_t)pn.B * ((pn.M + TILE - 1) / TILE) * 2 <= 0x7fffffffLL;

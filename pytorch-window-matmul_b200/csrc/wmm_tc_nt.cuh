@@ -34,15 +34,16 @@ struct NtParams {
   void *band;
 };
 
-template <int NH> struct NtSmem {
-  using OT = KMajorTile<NH>;
+template <int NH, int ES> struct NtSmem {
+  using OT = KMajorTileE<NH, ES>;
+  static constexpr bool BIG = OT::BYTES >= 32768;   // a 32 KB operand tile: N = 128 in 16 bits, N = 64 in fp32
   static constexpr int QS = 2;
-  static constexpr int KS = NH >= 128 ? 3 : 4;
-  static constexpr int STAGE_HALF = TILE * 128;  // 128 lines x 64 columns x 2 bytes
+  static constexpr int KS = BIG ? 3 : 4;
+  static constexpr int STAGE_HALF = TILE * 128;  // one staging box: 128 lines of 128 bytes (64 16-bit or 32 fp32 positions)
   // Staging boxes: a pool shared by the four epilogue groups, used in item order (item n of the CTA goes through box
   // n % STAGE_BOXES).  With more boxes than groups a group converts its next item while the stores of earlier ones
   // still wait their turn in the SM's store queue.
-  static constexpr int STAGE_BOXES = NH >= 128 ? 4 : 8;
+  static constexpr int STAGE_BOXES = BIG ? 4 : 8;
   static constexpr int STORE_DEPTH = STAGE_BOXES / 2;   // stores whose shared-memory read may be pending when the next is issued
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + QS * OT::BYTES;
@@ -85,12 +86,19 @@ __device__ __forceinline__ void mask_columns(uint32_t (&v)[32], int kbase, int k
 // MN-major B operand; otherwise Y rows are contiguous in the hidden index and the operand is K-major.
 // PAIRED: 2w is a multiple of 128, so the first and the last chunk of a tile are merged (a compile-time switch: each
 // variant carries only the epilogue paths it can reach, which keeps the loop body small).
-template <bool BF16, int NH, bool YMN, bool PAIRED>
+// ET: 0 = fp16, 1 = bf16, 2 = fp32 operands multiplied as tf32 (fp32 band; K-major operands and unpaired epilogue only).
+template <int ET, int NH, bool YMN, bool PAIRED>
 __global__ void __launch_bounds__(NT_THREADS, 1)
 band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
                   const __grid_constant__ CUtensorMap map_band, const NtParams p) {
-  using S = NtSmem<NH>;
-  using OT = KMajorTile<NH>;
+  constexpr bool F32 = ET == 2;
+  constexpr bool BF16 = ET == 1;
+  constexpr int ES = F32 ? 4 : 2;
+  constexpr int ITEM = 128 / ES;      // positions per epilogue item = per staging box line: 64 or 32
+  constexpr int IPC = CHUNK / ITEM;   // items per chunk: 2 or 4
+  static_assert(!(F32 && (PAIRED || YMN)), "the fp32 variant has neither the merged epilogue nor position-major operands");
+  using S = NtSmem<NH, ES>;
+  using OT = KMajorTileE<NH, ES>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t *base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -123,13 +131,13 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   // Items of a tile whose box lies wholly inside the band go through a staging box and a TMA store: all of them with
   // pairing; otherwise the halves of chunks 1 .. floor((2w - 127) / 128).  They are consecutive: items st_first ..
   // st_first + st_count - 1 of every tile.
-  const int st_first = paired ? 0 : 2;
-  const int st_count = paired ? 2 * (p.nchunks - 1) : 2 * max(0, (2 * p.w - (CHUNK - 1)) / CHUNK);
+  const int st_first = paired ? 0 : IPC;
+  const int st_count = paired ? IPC * (p.nchunks - 1) : IPC * max(0, (2 * p.w - (CHUNK - 1)) / CHUNK);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::QS; s++) { mbar_init(bar_q_full(s), 1); mbar_init(bar_q_empty(s), 1); }
     for (int s = 0; s < S::KS; s++) { mbar_init(bar_k_full(s), 1); mbar_init(bar_k_empty(s), 1); }
-    for (int s = 0; s < ACC_STAGES; s++) { mbar_init(bar_acc_full(s), 1); mbar_init(bar_acc_empty(s), 2 * EPI_THREADS); }
+    for (int s = 0; s < ACC_STAGES; s++) { mbar_init(bar_acc_full(s), 1); mbar_init(bar_acc_empty(s), IPC * EPI_THREADS); }
     for (int x = 0; x < S::STAGE_BOXES; x++) mbar_init(bar_st_full(x), EPI_THREADS);
     *st_freed = 0;
     *abort_flag = 0;
@@ -192,7 +200,7 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     // stage are converted by two epilogue groups; the stage is free again when both have read it.  With pairing the
     // first and the last chunk of a tile are multiplied back to back, so that both triangles are in TMEM together.
     if (lane == 0) {
-      constexpr uint32_t IDESC = instr_desc_f16(BF16, false, YMN, TILE, CHUNK);
+      constexpr uint32_t IDESC = F32 ? instr_desc_tf32(false, false, TILE, CHUNK) : instr_desc_f16(BF16, false, YMN, TILE, CHUNK);
       // MN-major Y: one box = NH rows (hidden) of 64 positions (128 B); 8-row groups 1024 B apart, a k-step of
       // 16 hidden rows is 2048 B further; the second 64 positions of the chunk are the second box (leading offset).
       constexpr uint64_t YDESC = YMN ? smem_desc_base(OT::BYTES / 2, 1024, 2u) : OT::DESC;
@@ -203,9 +211,12 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         if (!mbar_wait(bar_acc_empty(as), ((ait / ACC_STAGES) & 1) ^ 1, abort_flag)) return false;
         tc_fence_after_sync();
 #pragma unroll
-        for (int s = 0; s < OT::KSTEPS; s++)
-          umma_f16(tmem_base + as * CHUNK, smem_desc(OT::DESC, q_addr + OT::kstep_offset(s)),
-                   smem_desc(YDESC, k_addr + (YMN ? (uint32_t)s * 2048u : OT::kstep_offset(s))), IDESC, s > 0 ? 1u : 0u);
+        for (int s = 0; s < OT::KSTEPS; s++) {
+          const uint64_t da = smem_desc(OT::DESC, q_addr + OT::kstep_offset(s));
+          const uint64_t db = smem_desc(YDESC, k_addr + (YMN ? (uint32_t)s * 2048u : OT::kstep_offset(s)));
+          if (F32) umma_tf32(tmem_base + as * CHUNK, da, db, IDESC, s > 0 ? 1u : 0u);
+          else umma_f16(tmem_base + as * CHUNK, da, db, IDESC, s > 0 ? 1u : 0u);
+        }
         umma_commit(bar_acc_full(as));
         ++ait;
         return true;
@@ -250,13 +261,13 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     int seen = 0;   // items this group has taken so far: picks the verdict word
     const uint32_t lane_sel = (uint32_t)(quarter * 32) << 16;
     const int W = 2 * p.w + 1;
-    const int items_per_tile = 2 * (paired ? p.nchunks - 1 : p.nchunks);
+    const int items_per_tile = IPC * (paired ? p.nchunks - 1 : p.nchunks);
     uint16_t *band = static_cast<uint16_t *>(p.band);
     int cit = 0, iit = 0, rot = 0;  // chunks (accumulator stages) of earlier tiles / half-chunk items seen so far / group rotation
     // Items go to the groups round-robin over the CTA's whole item sequence.  When a tile has a multiple of four items,
     // its first two (the merged ones, the costliest) would always land on groups 0 and 1: the assignment is then
     // shifted by two from tile to tile.
-    const int rot_step = (items_per_tile % EPI_GROUPS) == 0 ? 2 : 0;
+    const int rot_step = (paired && (items_per_tile % EPI_GROUPS) == 0) ? 2 : 0;
     int tl = 0;   // tiles of this CTA so far
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x) {
@@ -268,7 +279,7 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       // costs two jumps across it.
       const int tile_iit = iit;   // items of earlier tiles
       for (int hitem = (grp - tile_iit - rot) & (EPI_GROUPS - 1); hitem < items_per_tile; hitem += EPI_GROUPS) {
-        const int item = hitem >> 1, h = hitem & 1;
+        const int item = hitem / IPC, h = hitem % IPC;
         const bool pair_item = paired && item == 0;
         // stage of this item's chunk: with pairing the tile's stages hold chunks 0, last, 1, 2, ... in this order
         const int a0 = cit + (paired ? (item == 0 ? 0 : item + 1) : item);
@@ -292,7 +303,7 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         named_bar_sync(bar_id, EPI_THREADS);
         if (!(ok = (*verdict != 0))) break;
         tc_fence_after_sync();
-        const uint32_t taddr = tmem_base + as * CHUNK + h * HALF + lane_sel;  // columns 64*h .. of chunk c
+        const uint32_t taddr = tmem_base + as * CHUNK + h * ITEM + lane_sel;  // columns ITEM*h .. of chunk c
         // positions of chunk c inside the sequence: columns kk in [kk_lo, kk_hi)
         const int p0 = r0 - p.w + p.off + c * CHUNK;
         const int kk_lo = p.lo - p0, kk_hi = p.hi - p0;
@@ -383,26 +394,60 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           mbar_arrive(bar_acc_empty(as));
           mbar_arrive(bar_acc_empty(as2));
         } else if (staged) {
-          // ---- half of a chunk that lies wholly inside the band ----
-          uint32_t va[32], vb[32];
-          tmem_ld_x32(taddr, va);
-          tmem_ld_x32(taddr + 32, vb);
-          tmem_ld_wait();
-          // the values are in registers: the accumulator half is free for the next chunk before the conversion starts
-          tc_fence_before_sync();
-          mbar_arrive(bar_acc_empty(as));
-          if (edge) {
-            mask_columns(va, h * 64, kk_lo, kk_hi);
-            mask_columns(vb, h * 64 + 32, kk_lo, kk_hi);
+          // ---- an item (half or quarter of a chunk) that lies wholly inside the band ----
+          if constexpr (F32) {
+            uint32_t va[32];
+            tmem_ld_x32(taddr, va);
+            tmem_ld_wait();
+            // the values are in registers: the accumulator columns are free for the next chunk before the staging starts
+            tc_fence_before_sync();
+            mbar_arrive(bar_acc_empty(as));
+            if (edge) mask_columns(va, h * ITEM, kk_lo, kk_hi);
+#pragma unroll
+            for (int q8 = 0; q8 < 8; q8++)
+              st_shared_v4(stage_addr(stage, rr, q8), make_uint4(va[4 * q8], va[4 * q8 + 1], va[4 * q8 + 2], va[4 * q8 + 3]));
+          } else {
+            uint32_t va[32], vb[32];
+            tmem_ld_x32(taddr, va);
+            tmem_ld_x32(taddr + 32, vb);
+            tmem_ld_wait();
+            // the values are in registers: the accumulator half is free for the next chunk before the conversion starts
+            tc_fence_before_sync();
+            mbar_arrive(bar_acc_empty(as));
+            if (edge) {
+              mask_columns(va, h * 64, kk_lo, kk_hi);
+              mask_columns(vb, h * 64 + 32, kk_lo, kk_hi);
+            }
+#pragma unroll
+            for (int q4 = 0; q4 < 4; q4++) st_shared_v4(stage_addr(stage, rr, q4), pack8<BF16>(&va[q4 * 8]));
+#pragma unroll
+            for (int q4 = 0; q4 < 4; q4++) st_shared_v4(stage_addr(stage, rr, 4 + q4), pack8<BF16>(&vb[q4 * 8]));
           }
-#pragma unroll
-          for (int q4 = 0; q4 < 4; q4++) st_shared_v4(stage_addr(stage, rr, q4), pack8<BF16>(&va[q4 * 8]));
-#pragma unroll
-          for (int q4 = 0; q4 < 4; q4++) st_shared_v4(stage_addr(stage, rr, 4 + q4), pack8<BF16>(&vb[q4 * 8]));
         } else if (!PAIRED) {
           // ---- triangular / ragged chunk of an unpaired window: predicated stores from registers.
           // Groups of 8 columns start on 16-byte boundaries of the band tensor, so whole groups go out
           // as one 16-byte store.
+          if constexpr (F32) {
+            // (groups of 4 fp32 columns are the 16-byte units)
+            float *row = static_cast<float *>(p.band) + ((int64_t)b * p.M + i) * W;
+            uint32_t v[32];
+            tmem_ld_x32(taddr, v);
+            tmem_ld_wait();
+            if (edge) mask_columns(v, h * ITEM, kk_lo, kk_hi);
+            if (rows_ok) {
+#pragma unroll
+              for (int q8 = 0; q8 < 8; q8++) {
+                const int j0 = c * CHUNK + h * ITEM + q8 * 4 - rr;
+                if (j0 >= 0 && j0 + 3 <= 2 * p.w) {
+                  *reinterpret_cast<uint4 *>(row + j0) = make_uint4(v[4 * q8], v[4 * q8 + 1], v[4 * q8 + 2], v[4 * q8 + 3]);
+                } else if (j0 + 3 >= 0 && j0 <= 2 * p.w) {
+#pragma unroll
+                  for (int e = 0; e < 4; e++)
+                    if (j0 + e >= 0 && j0 + e <= 2 * p.w) row[j0 + e] = __uint_as_float(v[4 * q8 + e]);
+                }
+              }
+            }
+          } else {
           uint16_t *row = band + ((int64_t)b * p.M + i) * W;
 #pragma unroll
           for (int gb = 0; gb < 2; gb++) {
@@ -424,6 +469,7 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 }
               }
             }
+          }
           }
           tc_fence_before_sync();
           mbar_arrive(bar_acc_empty(as));
@@ -449,10 +495,10 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         const int b = tile / p.tiles_per_batch, r0 = (tile % p.tiles_per_batch) * TILE;
         for (int k = 0; k < st_count; ++k, ++sidx) {
           const int hitem = st_first + k;
-          const int c = (paired && hitem < 2) ? 0 : (hitem >> 1), h = hitem & 1;
+          const int c = (paired && hitem < IPC) ? 0 : (hitem / IPC), h = hitem % IPC;
           const int sx = sidx % S::STAGE_BOXES;
           if (!(ok = mbar_wait(bar_st_full(sx), (sidx / S::STAGE_BOXES) & 1, abort_flag))) break;
-          tma_store_3d(&map_band, base + S::OFF_STAGE + (uint32_t)sx * S::STAGE_HALF, r0 + c * CHUNK + h * 64, r0, b);  // x = i + j of the box's first column
+          tma_store_3d(&map_band, base + S::OFF_STAGE + (uint32_t)sx * S::STAGE_HALF, r0 + c * CHUNK + h * ITEM, r0, b);  // x = i + j of the box's first column
           bulk_commit();
           if (sidx == 0) WMM_TRACE_POINT(8);
           if (sidx >= S::STORE_DEPTH) {

@@ -19,6 +19,7 @@ FLAG_FORCE_GENERIC = 1 << 1
 FLAG_REQUIRE_TENSOR = 1 << 2
 FLAG_SOFTMAX_KEEP_PADDING = 1 << 3
 FLAG_PREFER_SWEEP = 1 << 4
+FLAG_TF32 = 1 << 5
 BAND_NT, BAND_N, BAND_T = 1, 2, 3
 
 _DTYPES = {torch.float16: F16, torch.bfloat16: BF16, torch.float32: F32, torch.float64: F64}

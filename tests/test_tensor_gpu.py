@@ -336,3 +336,88 @@ def test_tensor_kernels_from_a_fresh_thread(wm):
     torch.cuda.synchronize()
     assert "error" not in result, result.get("error")
     assert torch.equal(result["a"], wm.band_nt(q, q, 64, flags=N.FLAG_REQUIRE_TENSOR))
+
+
+# ---- fp32 operands on the tensor cores (WMM_FLAG_TF32) -------------------------------------------------------------
+TF32_REL = 2e-3
+TF32_SHAPES = [(2, 512, 64, 64), (1, 1024, 64, 256), (2, 200, 64, 64), (3, 136, 64, 4), (1, 640, 64, 12), (4, 256, 32, 8),
+               (1, 768, 64, 384), (2, 8, 64, 4), (2, 384, 32, 128), (1, 1152, 64, 100)]
+
+
+def _assert_tf32_close(got, want, what):
+    """2e-3 relative in the norm the target names (largest error against the largest reference value, reported), and
+    element by element |err| <= 3e-3 (|x| + rms): the tensor core drops the low 13 mantissa bits of each fp32 operand
+    (it truncates, it does not round), so every product is low by up to 2e-3 of itself."""
+    g = got.detach().double().cpu().numpy()
+    w_ = want.astype(np.float64)
+    worst = np.abs(g - w_).max() / max(np.abs(w_).max(), 1e-30)
+    assert worst <= TF32_REL, "%s: max abs err / max abs ref = %.3e" % (what, worst)
+    H.assert_lowp_close(got, want, what, rel=1.5 * TF32_REL)
+
+
+@pytest.mark.parametrize("shape", TF32_SHAPES)
+def test_band_nt_tf32(wm, shape):
+    """fp32 inputs multiplied as tf32 (10-bit mantissas, fp32 sums) against the fp32 oracle on the same inputs: within
+    2e-3 relative, exact zeros outside the sequence, every entry written, and the tensor-core kernel really taken."""
+    from window_matmul import _native as N
+
+    B, M, Nn, w = shape
+    d = H.rand_inputs(B, M, Nn, w, seed=7, scale=1.0 / np.sqrt(Nn))
+    want = H.oracle.window_matmul_forward(d["q"], np.ascontiguousarray(d["kt"].transpose(0, 2, 1)), w)
+    q, kt = H.to_dev(d["q"], torch.float32), H.to_dev(d["kt"], torch.float32)
+    band = torch.full((B, M, 2 * w + 1), float("nan"), dtype=torch.float32, device="cuda")
+    flags = N.FLAG_TF32 | N.FLAG_REQUIRE_TENSOR
+    assert N.lib.wmm_query_path(N.BAND_NT, N.operand(q), N.operand(kt), band.data_ptr(), N.geometry(B, M, Nn, w), N.F32, flags) == 1
+    assert N.lib.wmm_query_path(N.BAND_NT, N.operand(q), N.operand(kt), band.data_ptr(), N.geometry(B, M, Nn, w), N.F32, 0) == 0
+    wm.band_nt(q, kt, w, out=band, flags=flags)
+    torch.cuda.synchronize()
+    assert N.device_status() == 0
+    _assert_tf32_close(band, want, "band_nt tf32 %s" % (shape,))
+    mask = H.out_of_sequence_mask(M, w)
+    assert (band.cpu().numpy()[:, mask] == 0).all()
+    # without the flag fp32 stays on the exact-order kernels (rtol 1e-5)
+    exact = wm.band_nt(q, kt, w)
+    H.assert_lowp_close(exact, want, "band_nt exact", rel=2e-5)
+
+
+@pytest.mark.parametrize("shape", TF32_SHAPES)
+def test_band_n_and_band_t_tf32(wm, shape):
+    """The other two contractions on fp32 tensors with WMM_FLAG_TF32, NaN in the out-of-sequence band slots (they must
+    never reach a product), against the fp32 oracle; then the two backward entry points, which take the same kernels."""
+    from window_matmul import _native as N
+
+    B, M, Nn, w = shape
+    d = H.rand_inputs(B, M, Nn, w, seed=8, scale=1.0 / np.sqrt(Nn))
+    mask = H.out_of_sequence_mask(M, w)
+    flags = N.FLAG_TF32 | N.FLAG_REQUIRE_TENSOR
+    att = d["att"].copy()
+    att[:, mask] = np.nan
+    att_d, v_d, go_d = H.to_dev(att, torch.float32), H.to_dev(d["v"], torch.float32), H.to_dev(d["g_out"], torch.float32)
+    want_o = H.oracle.unwindow_matmul_forward(d["att"], d["v"], w)
+    want_ga, want_gv = H.oracle.unwindow_matmul_backward(d["att"], d["v"], w, d["g_out"])
+    o = torch.full((B, M, Nn), float("nan"), device="cuda")
+    wm.band_n(att_d, v_d, w, out=o, flags=flags)
+    gv = torch.full((B, M, Nn), float("nan"), device="cuda")
+    wm.band_t(att_d, go_d, w, out=gv, flags=flags)
+    torch.cuda.synchronize()
+    assert N.device_status() == 0
+    _assert_tf32_close(o, want_o, "band_n tf32 %s" % (shape,))
+    _assert_tf32_close(gv, want_gv, "band_t tf32 %s" % (shape,))
+    # the reference-shaped backward calls under the process-wide flag
+    old = wm.set_flags(N.FLAG_TF32)
+    try:
+        q_d, k_d = H.to_dev(d["q"], torch.float32), H.to_dev(np.ascontiguousarray(d["kt"]), torch.float32).transpose(-1, -2)
+        gb = d["g_band"].copy()
+        gb[:, mask] = 0
+        gq, gk = wm.window_matmul_backward(q_d, k_d, w, H.to_dev(gb, torch.float32))
+        ga, gv2 = wm.unwindow_matmul_backward(att_d, v_d, w, go_d)
+    finally:
+        wm.set_flags(old)
+    torch.cuda.synchronize()
+    want_gq, want_gk = H.oracle.window_matmul_backward(d["q"], np.ascontiguousarray(d["kt"].transpose(0, 2, 1)), w, gb)
+    _assert_tf32_close(gq, want_gq, "grad_q tf32")
+    _assert_tf32_close(gk, want_gk, "grad_k tf32")
+    _assert_tf32_close(ga, want_ga, "grad_a tf32")
+    _assert_tf32_close(gv2, want_gv, "grad_v tf32")
+    assert (ga.cpu().numpy()[:, mask] == 0).all()
+    assert N.device_status() == 0
