@@ -28,7 +28,8 @@
  *   band_t :  Out [b,p,h] = sum_{i in [0,rows), 0 <= j <= 2*window} Band[b,i,j] * X[b,i,h]
  *                           for seq_lo <= p < seq_hi; rows p of Out outside that range are zeros
  *
- * X and Band have `rows` rows; Y (band_nt, band_n) and Out of band_t have `other_rows` rows.  The
+ * X and Band have `rows` rows (batch entries of the band `band_stride_b` elements apart, by default contiguous); Y
+ * (band_nt, band_n) and Out of band_t have `other_rows` rows.  The
  * plain, unsharded operators use other_rows = rows, other_off = 0, seq_lo = 0, seq_hi = rows.  A
  * sequence-sharded caller passes its local rows plus a halo: other_rows = rows + 2*window,
  * other_off = window, and seq_lo/seq_hi clip at the ends of the global sequence.
@@ -48,7 +49,7 @@
 extern "C" {
 #endif
 
-#define WMM_ABI_VERSION 2
+#define WMM_ABI_VERSION 3
 
 #if defined(__GNUC__)
 #define WMM_API __attribute__((visibility("default")))
@@ -113,6 +114,9 @@ typedef struct wmm_geometry {
   int32_t other_off;  /* position of band entry (i=0, j=window) in that row space */
   int32_t seq_lo;     /* positions seq_lo <= p < seq_hi are inside the sequence */
   int32_t seq_hi;
+  int64_t band_stride_b; /* elements between batch entries of the band tensor; 0 = rows * (2*window+1), i.e. contiguous.
+                          * A larger stride addresses a range of rows of a longer band tensor (the interior rows of a
+                          * sequence shard, say) in place; only the tensor-core kernels take it. */
 } wmm_geometry;
 
 /* ---- library / diagnostics ------------------------------------------------------------------- */

@@ -42,6 +42,9 @@ int check_geometry(const wmm_geometry *g, int dtype, unsigned flags) {
       (int64_t)g->other_rows + 2ll * g->window + 256 > 0x7fffffffLL ||
       (int64_t)(g->other_off < 0 ? -(int64_t)g->other_off : g->other_off) > (1ll << 30))
     return fail(WMM_ERR_TOO_LARGE, "extent beyond the 31-bit index range");
+  if (g->band_stride_b != 0 && g->band_stride_b < (int64_t)g->rows * (2ll * g->window + 1))
+    return fail(WMM_ERR_STRIDE, "band batch stride %lld is smaller than a batch entry (%d rows of %d)", (long long)g->band_stride_b,
+                g->rows, 2 * g->window + 1);
   if ((flags & WMM_FLAG_FORCE_GENERIC) && (flags & WMM_FLAG_REQUIRE_TENSOR))
     return fail(WMM_ERR_UNSUPPORTED, "FORCE_GENERIC and REQUIRE_TENSOR exclude each other");
   if ((flags & WMM_FLAG_SPLIT_ROUNDING) && (flags & WMM_FLAG_REQUIRE_TENSOR))
@@ -68,6 +71,7 @@ void fill(wmm::Problem &p, const wmm_geometry *g, int dtype, unsigned flags) {
   p.off = g->other_off;
   p.lo = g->seq_lo;
   p.hi = g->seq_hi;
+  p.band_sb = g->band_stride_b ? g->band_stride_b : (int64_t)g->rows * (2ll * g->window + 1);
   p.dtype = dtype;
   p.flags = flags;
 }
@@ -113,6 +117,8 @@ int dispatch(wmm::Primitive prim, const wmm::Problem &p, void *stream) {
   const int family = pick_family(prim, p);
   if (family == 0 && (p.flags & WMM_FLAG_REQUIRE_TENSOR))
     return fail(WMM_ERR_UNSUPPORTED, "no tensor-core kernel takes this problem (primitive %d)", (int)prim);
+  if (family != 1 && p.band_sb != (int64_t)p.M * (2ll * p.w + 1))
+    return fail(WMM_ERR_STRIDE, "a band with a batch stride is taken by the tensor-core kernels only (primitive %d)", (int)prim);
   int launches = 0;
   cudaError_t e = family == 1   ? wmm::launch_tensor(prim, p, (cudaStream_t)stream, &launches)
                   : family == 2 ? wmm::launch_small(prim, p, (cudaStream_t)stream, &launches)
@@ -201,6 +207,8 @@ static int band_softmax_common(bool backward, const void *in, const void *in2, v
   if (flags & ~(unsigned)WMM_FLAG_SOFTMAX_KEEP_PADDING)
     return fail(WMM_ERR_UNSUPPORTED, "the band softmax takes no flag but WMM_FLAG_SOFTMAX_KEEP_PADDING");
   if ((int64_t)g->batch * g->rows == 0) return WMM_OK;
+  if (g->band_stride_b != 0 && g->band_stride_b != (int64_t)g->rows * (2ll * g->window + 1))
+    return fail(WMM_ERR_STRIDE, "the band softmax takes contiguous band tensors only");
   if (!in || !out || (backward && !in2)) return fail(WMM_ERR_NULL, "a band pointer is NULL");
   if (((uintptr_t)in | (uintptr_t)out | (uintptr_t)in2) & 15)
     return fail(WMM_ERR_STRIDE, "band tensors of the softmax must be 16-byte aligned");

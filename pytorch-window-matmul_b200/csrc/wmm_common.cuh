@@ -22,6 +22,7 @@ struct Problem {
   int64_t o_sb, o_sr, o_sc;
   int32_t B, M, N, w;      // batch, rows of X / band, hidden size, window
   int32_t Mo, off, lo, hi; // rows of the other row space, its offset, in-sequence range
+  int64_t band_sb;         // elements between batch entries of the band (M * (2w+1) when contiguous)
   int32_t dtype;
   uint32_t flags;
 };

@@ -263,10 +263,11 @@ bool make_operand_map_mn(CUtensorMap *m, bool bf16, const void *data, int cols, 
 // The band as a pitched matrix: x = i + j in [0, M + 2w), row i with pitch 2w elements, batch with
 // pitch M*(2w+1).  Rows overlap in memory by design (pitch < extent); an in-range (x, i, b) never
 // addresses memory outside the tensor.  Box = (64 x 128 x 1), 128-byte swizzle.
-bool make_band_map(CUtensorMap *m, int et, const void *band, int M, int w, int batch, int box_rows = 128, bool atom32 = false) {
+bool make_band_map(CUtensorMap *m, int et, const void *band, int M, int w, int batch, int64_t band_sb, int box_rows = 128,
+                   bool atom32 = false) {
   const int es = et == 2 ? 4 : 2;
   const cuuint64_t dims[3] = {(cuuint64_t)M + 2ull * w, (cuuint64_t)M, (cuuint64_t)batch};
-  const cuuint64_t strides[2] = {(cuuint64_t)(2 * w) * es, (cuuint64_t)M * (2ull * w + 1) * es};
+  const cuuint64_t strides[2] = {(cuuint64_t)(2 * w) * es, (cuuint64_t)band_sb * es};
   const cuuint32_t box[3] = {(cuuint32_t)(128 / es), (cuuint32_t)box_rows, 1};   // 128-byte lines
   const cuuint32_t estr[3] = {1, 1, 1};
   const CUresult r = encode_fn()(m, map_dtype(et), 3,
@@ -293,7 +294,8 @@ bool y_position_major(const Problem &p) {
          ((p.w - p.off) % 8) == 0;
 }
 
-bool band_tma_ok(const void *band, int M, int w) { return aligned16(band) && (w % 4) == 0 && w >= 4 && (M % 8) == 0; }
+// (the batch stride must be a multiple of 16 bytes: of 8 elements, which also covers fp32)
+bool band_tma_ok(const void *band, int64_t band_sb, int w) { return aligned16(band) && (w % 4) == 0 && w >= 4 && (band_sb % 8) == 0; }
 
 template <int ET, int NH, bool YMN, bool PAIRED> cudaError_t launch_nt(const Problem &p, cudaStream_t stream) {
   constexpr int BF16 = ET;   // (element type code of the tensor maps)
@@ -306,6 +308,7 @@ template <int ET, int NH, bool YMN, bool PAIRED> cudaError_t launch_nt(const Pro
   k.nchunks = (TILE + 2 * p.w + CHUNK - 1) / CHUNK;
   k.paired = PAIRED ? 1 : 0;
   k.band = p.o;
+  k.band_sb = p.band_sb;
   auto kern = band_nt_tc_kernel<ET, NH, YMN, PAIRED>;
   // the attribute is per device; setting it on every call is cheap and needs no per-device cache
   cudaError_t attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::ALLOC);
@@ -319,7 +322,7 @@ template <int ET, int NH, bool YMN, bool PAIRED> cudaError_t launch_nt(const Pro
   if (!make_operand_map(&mx, BF16, p.a, NH, p.M, p.B, p.a_sr, p.a_sb, OT::BOXK) ||
       !(YMN ? make_operand_map_mn(&my, BF16, p.b, NH, p.Mo, p.B, p.b_sc, p.b_sb)
             : make_operand_map(&my, BF16, p.b, NH, p.Mo, p.B, p.b_sr, p.b_sb, OT::BOXK)) ||
-      !make_band_map(&mb, BF16, p.o, p.M, p.w, p.B))
+      !make_band_map(&mb, BF16, p.o, p.M, p.w, p.B, p.band_sb))
     return cudaErrorInvalidValue;
   const int grid = persistent_grid(k.total_tiles);
   set_launch_detail("band_nt launch, grid %d", grid);
@@ -362,7 +365,7 @@ template <bool BF16, int NH, int MODE, bool YMN> cudaError_t launch_mm(const Pro
   }
   // (the tensor maps need the current context the runtime call above has bound to this thread)
   CUtensorMap mband, mother0, mout0, mother1, mout1;
-  if (!make_band_map(&mband, BF16, p.a, p.M, p.w, p.B) ||
+  if (!make_band_map(&mband, BF16, p.a, p.M, p.w, p.B, p.band_sb) ||
       !(YMN ? make_operand_map_mn(&mother0, BF16, p.b, NH, other_rows, p.B, p.b_sc, p.b_sb)
             : make_operand_map(&mother0, BF16, p.b, NH, other_rows, p.B, p.b_sr, p.b_sb, OT::BOXK)) ||
       !make_operand_map(&mout0, BF16, p.o, NH, out_rows, p.B, p.o_sr, p.o_sb, OT::BOXK))
@@ -410,7 +413,7 @@ template <int NH, bool TR> cudaError_t launch_mm32(const Problem &p, cudaStream_
   }
   CUtensorMap mband, mother, mout;
   // MN-major fp32 operands (the other operand; the band box of band_t) use the 128-byte swizzle with 32-byte atoms
-  if (!make_band_map(&mband, 2, p.a, p.M, p.w, p.B, TR ? M32_RC : 128, TR) ||
+  if (!make_band_map(&mband, 2, p.a, p.M, p.w, p.B, p.band_sb, TR ? M32_RC : 128, TR) ||
       !make_operand_map(&mother, 2, p.b, NH, other_rows, p.B, p.b_sr, p.b_sb, 32, M32_RC, true) ||
       !make_operand_map(&mout, 2, p.o, NH, out_rows, p.B, p.o_sr, p.o_sb, 32, 128))
     return cudaErrorInvalidValue;
@@ -453,7 +456,7 @@ template <bool BF16, int NH> cudaError_t launch_sweep(const Problem &pn, const P
   k.gq = static_cast<uint16_t *>(pn.o); k.gq_sb = pn.o_sb; k.gq_sr = pn.o_sr;
   k.gk = static_cast<uint16_t *>(pt.o); k.gk_sb = pt.o_sb; k.gk_sr = pt.o_sr;
   CUtensorMap mband, my, mx;
-  if (!make_band_map(&mband, BF16, pn.a, pn.M, pn.w, pn.B) ||
+  if (!make_band_map(&mband, BF16, pn.a, pn.M, pn.w, pn.B, pn.band_sb) ||
       !make_operand_map(&my, BF16, pn.b, NH, pn.Mo, pn.B, pn.b_sr, pn.b_sb, OT::BOXK) ||
       !make_operand_map(&mx, BF16, pt.b, NH, pt.M, pt.B, pt.b_sr, pt.b_sb, OT::BOXK))
     return cudaErrorInvalidValue;
@@ -472,13 +475,13 @@ bool tensor_eligible(Primitive prim, const Problem &p) {
     if ((int64_t)p.B * ((p.M + TILE - 1) / TILE) > 0x7fffffffLL) return false;
     // element strides of fp32 operands: multiples of 4 would do; the 16-bit rule (multiples of 8) is kept
     if (prim == BAND_NT)
-      return band_tma_ok(p.o, p.M, p.w) && operand_tma_ok(p.a, p.a_sb, p.a_sr, p.a_sc, p.B) &&
+      return band_tma_ok(p.o, p.band_sb, p.w) && operand_tma_ok(p.a, p.a_sb, p.a_sr, p.a_sc, p.B) &&
              operand_tma_ok(p.b, p.b_sb, p.b_sr, p.b_sc, p.B) && p.Mo > 0;
     if (prim == BAND_N)
-      return band_tma_ok(p.a, p.M, p.w) && operand_tma_ok(p.b, p.b_sb, p.b_sr, p.b_sc, p.B) &&
+      return band_tma_ok(p.a, p.band_sb, p.w) && operand_tma_ok(p.b, p.b_sb, p.b_sr, p.b_sc, p.B) &&
              operand_tma_ok(p.o, p.o_sb, p.o_sr, p.o_sc, p.B) && p.Mo > 0;
     // band_t: the box of a tile starts at x = t0 - off + w, a multiple of 4 elements (16 bytes)
-    return band_tma_ok(p.a, p.M, p.w) && ((p.w - p.off) % 4) == 0 && operand_tma_ok(p.b, p.b_sb, p.b_sr, p.b_sc, p.B) &&
+    return band_tma_ok(p.a, p.band_sb, p.w) && ((p.w - p.off) % 4) == 0 && operand_tma_ok(p.b, p.b_sb, p.b_sr, p.b_sc, p.B) &&
            operand_tma_ok(p.o, p.o_sb, p.o_sr, p.o_sc, p.B) && p.M > 0;
   }
   if (p.dtype != WMM_F16 && p.dtype != WMM_BF16) return false;
@@ -487,15 +490,15 @@ bool tensor_eligible(Primitive prim, const Problem &p) {
   if ((int64_t)p.B * ((p.M + TILE - 1) / TILE) > 0x7fffffffLL) return false;
   switch (prim) {
     case BAND_NT:
-      return band_tma_ok(p.o, p.M, p.w) && operand_tma_ok(p.a, p.a_sb, p.a_sr, p.a_sc, p.B) &&
+      return band_tma_ok(p.o, p.band_sb, p.w) && operand_tma_ok(p.a, p.a_sb, p.a_sr, p.a_sc, p.B) &&
              (operand_tma_ok(p.b, p.b_sb, p.b_sr, p.b_sc, p.B) || y_position_major(p)) && p.Mo > 0;
     case BAND_N:
-      return band_tma_ok(p.a, p.M, p.w) &&
+      return band_tma_ok(p.a, p.band_sb, p.w) &&
              (operand_tma_ok(p.b, p.b_sb, p.b_sr, p.b_sc, p.B) || (y_position_major(p) && p.lo == 0 && p.hi == p.Mo)) &&
              operand_tma_ok(p.o, p.o_sb, p.o_sr, p.o_sc, p.B) && p.Mo > 0;
     case BAND_T:
       // the box of a tile starts at x = t0 - off + w, which must be a multiple of 8 elements (16 bytes)
-      return band_tma_ok(p.a, p.M, p.w) && ((p.w - p.off) % 8) == 0 && operand_tma_ok(p.b, p.b_sb, p.b_sr, p.b_sc, p.B) &&
+      return band_tma_ok(p.a, p.band_sb, p.w) && ((p.w - p.off) % 8) == 0 && operand_tma_ok(p.b, p.b_sb, p.b_sr, p.b_sc, p.B) &&
              operand_tma_ok(p.o, p.o_sb, p.o_sr, p.o_sc, p.B) && p.M > 0;
     default: return false;
   }

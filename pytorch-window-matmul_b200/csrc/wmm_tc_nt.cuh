@@ -32,6 +32,7 @@ struct NtParams {
   int tiles_per_batch, total_tiles, nchunks;
   int paired;  // 2w is a multiple of 128: merge first and last chunk of a tile
   void *band;
+  int64_t band_sb;   // elements between batch entries of the band (rows written without TMA)
 };
 
 template <int NH, int ES> struct NtSmem {
@@ -319,7 +320,7 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           const int kl_lo = kk_lo - cl * CHUNK, kl_hi = kk_hi - cl * CHUNK;
           const bool edge_l = kl_lo > 0 || kl_hi < CHUNK;
           const bool direct_l = (rr == vr - 1);  // last valid row: its last-chunk piece has no staging line
-          uint16_t *row_l = band + ((int64_t)b * p.M + i) * W + (cl * CHUNK - rr);
+          uint16_t *row_l = band + (int64_t)b * p.band_sb + (int64_t)i * W + (cl * CHUNK - rr);
 #pragma unroll
           for (int gb = 0; gb < 2; gb++) {
             const int g = 2 * h + gb;
@@ -429,7 +430,7 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           // as one 16-byte store.
           if constexpr (F32) {
             // (groups of 4 fp32 columns are the 16-byte units)
-            float *row = static_cast<float *>(p.band) + ((int64_t)b * p.M + i) * W;
+            float *row = static_cast<float *>(p.band) + (int64_t)b * p.band_sb + (int64_t)i * W;
             uint32_t v[32];
             tmem_ld_x32(taddr, v);
             tmem_ld_wait();
@@ -448,7 +449,7 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
               }
             }
           } else {
-          uint16_t *row = band + ((int64_t)b * p.M + i) * W;
+          uint16_t *row = band + (int64_t)b * p.band_sb + (int64_t)i * W;
 #pragma unroll
           for (int gb = 0; gb < 2; gb++) {
             const int g = 2 * h + gb;

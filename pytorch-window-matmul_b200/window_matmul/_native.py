@@ -44,6 +44,7 @@ class Geometry(ctypes.Structure):
         ("other_off", ctypes.c_int32),
         ("seq_lo", ctypes.c_int32),
         ("seq_hi", ctypes.c_int32),
+        ("band_stride_b", ctypes.c_int64),
     ]
 
 
@@ -96,8 +97,8 @@ def _load():
     lib.wmm_band_softmax.argtypes = [vp, vp, P(Geometry), i32, ctypes.c_float, u32, vp]
     lib.wmm_band_softmax_bwd.restype = i32
     lib.wmm_band_softmax_bwd.argtypes = [vp, vp, vp, P(Geometry), i32, ctypes.c_float, u32, vp]
-    if lib.wmm_version() != 2:
-        raise RuntimeError("window_matmul: %s has ABI version %d, expected 2" % (LIB_PATH, lib.wmm_version()))
+    if lib.wmm_version() != 3:
+        raise RuntimeError("window_matmul: %s has ABI version %d, expected 3" % (LIB_PATH, lib.wmm_version()))
     return lib
 
 
@@ -119,10 +120,10 @@ def operand(t: torch.Tensor, swap_inner: bool = False) -> Operand:
     return Operand(t.data_ptr(), sb, sr, sc)
 
 
-def geometry(batch, rows, cols, window, other_rows=None, other_off=0, seq=None) -> Geometry:
+def geometry(batch, rows, cols, window, other_rows=None, other_off=0, seq=None, band_stride_b=0) -> Geometry:
     other_rows = rows if other_rows is None else other_rows
     lo, hi = (0, other_rows) if seq is None else seq
-    return Geometry(batch, rows, cols, window, other_rows, other_off, lo, hi)
+    return Geometry(batch, rows, cols, window, other_rows, other_off, lo, hi, band_stride_b)
 
 
 def stream_of(t: torch.Tensor) -> ctypes.c_void_p:

@@ -86,18 +86,31 @@ class PeerHalo:
         """Extended buffer for the partial gradient of operand i (what band_t writes with other_rows = rows + 2w)."""
         return self.store[self.count + i]
 
-    def _pull(self, part: int, accumulate: bool) -> None:
+    def _pull(self, part: int, accumulate: bool, which=None) -> None:
         with torch.cuda.device(self.device):
             stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
-            N.check(N.lib.wmm_halo_pull(self._bufs[part], self.count, ctypes.byref(self._flags), self.batch, self.rows, self.cols,
+            if which is None:
+                bufs, count = self._bufs[part], self.count
+            else:   # one tensor only (every rank must then exchange the same one)
+                bufs, count = (N.HaloBuffer * 1)(self._bufs[part][which]), 1
+            N.check(N.lib.wmm_halo_pull(bufs, count, ctypes.byref(self._flags), self.batch, self.rows, self.cols,
                                         self.window, N.dtype_code(self.store), 1 if accumulate else 0, stream))
 
-    def exchange(self) -> List[torch.Tensor]:
-        """Fills the margins of every operand with the neighbours' edge rows; returns the extended buffers."""
-        self._pull(0, False)
-        return [self.ext(i) for i in range(self.count)]
+    def exchange(self, which=None) -> List[torch.Tensor]:
+        """Fills the margins of every operand (or of operand `which`) with the neighbours' edge rows; returns the
+        extended buffers.  Runs on torch's current stream: issued on a side stream it overlaps work that needs no halo
+        (see interior_rows)."""
+        self._pull(0, False, which)
+        return [self.ext(i) for i in range(self.count)] if which is None else [self.ext(which)]
 
-    def reduce(self) -> List[torch.Tensor]:
+    def reduce(self, which=None) -> List[torch.Tensor]:
         """Adds the neighbours' partial rows for this rank's edge positions; returns this rank's gradient rows."""
-        self._pull(1, True)
-        return [self.partial(i)[:, self.window:self.window + self.rows] for i in range(self.count)]
+        self._pull(1, True, which)
+        idx = range(self.count) if which is None else [which]
+        return [self.partial(i)[:, self.window:self.window + self.rows] for i in idx]
+
+    def interior_rows(self) -> Tuple[int, int]:
+        """Rows [lo, hi) of this rank whose window touches no margin: a contraction over them needs no halo and can run
+        while the exchange is still in flight; rows [0, lo) and [hi, rows) wait for it.  (A row i reads the extended rows
+        i .. i + 2w; the margins are the first and last w of them.)"""
+        return self.window, self.rows - self.window

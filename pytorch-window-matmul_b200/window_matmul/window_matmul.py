@@ -50,11 +50,28 @@ def _check_out(out: torch.Tensor, shape, like: torch.Tensor, band: bool) -> torc
     (and, for the operand outputs, strides), so a wrong shape, dtype or device would be an out-of-bounds device write."""
     _mismatch(isinstance(out, torch.Tensor) and tuple(out.shape) == tuple(shape))
     _mismatch(out.dtype == like.dtype and out.device == like.device)
-    if band:        # band outputs are addressed as contiguous (B, M, 2w+1)
-        _mismatch(out.is_contiguous())
+    if band:        # band outputs: contiguous (B, M, 2w+1), or a range of rows of such a tensor (see _band_stride)
+        _mismatch(_band_stride(out) is not None)
     else:           # operand outputs go through their strides; elements must not overlap
         _mismatch(all(st > 0 for st, n in zip(out.stride(), out.shape) if n > 1))
     return out
+
+
+def _band_stride(t: torch.Tensor):
+    """Batch stride to pass for a band tensor (B, M, 2w+1): 0 for a contiguous one, the stride of dim 0 for a range of rows
+    cut out of a longer band tensor (rows and slots dense, batch entries further apart), None for anything else."""
+    if t.is_contiguous():
+        return 0
+    B, M, W = t.shape
+    if t.stride(2) == 1 and t.stride(1) == W and t.stride(0) >= M * W:
+        return t.stride(0)
+    return None
+
+
+def _band_in(t: torch.Tensor):
+    """A band operand as the kernels can read it: itself if dense or a row range of a dense tensor, else a copy."""
+    sb = _band_stride(t)
+    return (t, sb) if sb is not None else (t.contiguous(), 0)
 
 
 def _addressable(t: torch.Tensor) -> torch.Tensor:
@@ -75,7 +92,7 @@ def band_nt(x, y, window, *, other_off=0, seq=None, out=None, flags=None):
     _mismatch(y.dim() == 3 and y.shape[0] == B and y.shape[2] == Nn)
     shape = (B, M, 2 * window + 1)
     band = torch.empty(shape, dtype=x.dtype, device=x.device) if out is None else _check_out(out, shape, x, True)
-    g = N.geometry(B, M, Nn, window, y.shape[1], other_off, seq)
+    g = N.geometry(B, M, Nn, window, y.shape[1], other_off, seq, _band_stride(band))
     with torch.cuda.device(x.device):
         N.check(N.lib.wmm_band_nt(N.operand(x), N.operand(y), band.data_ptr(), g, N.dtype_code(x),
                                   _FLAGS if flags is None else flags, N.stream_of(x)))
@@ -85,12 +102,12 @@ def band_nt(x, y, window, *, other_off=0, seq=None, out=None, flags=None):
 def band_n(band, y, window, *, rows_out=None, other_off=0, seq=None, out=None, flags=None):
     """Out[b,i,:] = sum_j Band[b,i,j] Y[b,i+j-w+other_off,:].  band (B,M,2w+1), y (B,Mo,N) -> (B,M,N)."""
     _require_cuda(band, y)
-    band, y = band.contiguous(), _addressable(y)
+    (band, band_sb), y = _band_in(band), _addressable(y)
     B, M, W = band.shape
     _mismatch(W == 2 * window + 1 and y.dim() == 3 and y.shape[0] == B)
     Nn = y.shape[2]
     o = torch.empty((B, M, Nn), dtype=y.dtype, device=y.device) if out is None else _check_out(out, (B, M, Nn), y, False)
-    g = N.geometry(B, M, Nn, window, y.shape[1], other_off, seq)
+    g = N.geometry(B, M, Nn, window, y.shape[1], other_off, seq, band_sb)
     with torch.cuda.device(y.device):
         N.check(N.lib.wmm_band_n(band.data_ptr(), N.operand(y), N.operand(o), g, N.dtype_code(y),
                                  _FLAGS if flags is None else flags, N.stream_of(y)))
@@ -100,13 +117,13 @@ def band_n(band, y, window, *, rows_out=None, other_off=0, seq=None, out=None, f
 def band_t(band, x, window, *, other_rows=None, other_off=0, seq=None, out=None, flags=None):
     """Out[b,p,:] = sum_i Band[b,i,p-other_off-i+w] X[b,i,:].  band (B,M,2w+1), x (B,M,N) -> (B,Mo,N)."""
     _require_cuda(band, x)
-    band, x = band.contiguous(), _addressable(x)
+    (band, band_sb), x = _band_in(band), _addressable(x)
     B, M, W = band.shape
     _mismatch(W == 2 * window + 1 and x.dim() == 3 and x.shape[0] == B and x.shape[1] == M)
     Nn = x.shape[2]
     Mo = M if other_rows is None else other_rows
     o = torch.empty((B, Mo, Nn), dtype=x.dtype, device=x.device) if out is None else _check_out(out, (B, Mo, Nn), x, False)
-    g = N.geometry(B, M, Nn, window, Mo, other_off, seq)
+    g = N.geometry(B, M, Nn, window, Mo, other_off, seq, band_sb)
     with torch.cuda.device(x.device):
         N.check(N.lib.wmm_band_t(band.data_ptr(), N.operand(x), N.operand(o), g, N.dtype_code(x),
                                  _FLAGS if flags is None else flags, N.stream_of(x)))

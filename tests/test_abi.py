@@ -28,7 +28,7 @@ def test_library_exports_every_declared_symbol():
     lib = ctypes.CDLL(N.LIB_PATH)
     for name in _declared():
         assert hasattr(lib, name), name
-    assert lib.wmm_version() == 2
+    assert lib.wmm_version() == 3
 
 
 def test_argument_validation_needs_no_gpu():
@@ -60,6 +60,17 @@ def test_argument_validation_needs_no_gpu():
     assert N.lib.wmm_band_nt(op, op, None, N.geometry(0, 8, 4, 2), N.F32, 0, None) == 0
     assert N.launch_count() == before
     assert N.lib.wmm_status_string(-6) == b"WMM_ERR_CUDA"
+
+
+def test_band_batch_stride_validation_needs_no_gpu():
+    from window_matmul import _native as N
+
+    op = N.Operand(256, 64, 8, 1)
+    g = N.geometry(2, 8, 8, 2, band_stride_b=8 * 5 - 1)           # smaller than one batch entry of the band
+    assert N.lib.wmm_band_nt(op, op, 512, g, N.F32, 0, None) == -4
+    assert b"batch stride" in N.lib.wmm_last_error_string()
+    g = N.geometry(2, 8, 0, 2, band_stride_b=8 * 5 + 8)           # the softmax takes contiguous bands only
+    assert N.lib.wmm_band_softmax(256, 256, g, N.BF16, 1.0, 0, None) == -4
 
 
 def test_band_softmax_argument_validation_needs_no_gpu():
@@ -119,8 +130,8 @@ def test_public_header_is_plain_c_and_cxx(tmp_path):
     if not shutil.which("gcc") or not shutil.which("g++"):
         pytest.skip("no host compiler")
     src = tmp_path / "use.c"
-    src.write_text('#include "wmm_b200.h"\nint main(void) { wmm_geometry g = {1, 8, 4, 2, 8, 0, 0, 8}; wmm_operand o = {0, 32, 4, 1};\n'
-                   '  return (int)(g.window + o.stride_c) * 0 + (WMM_OK != 0) + (sizeof(wmm_geometry) != 32); }\n')
+    src.write_text('#include "wmm_b200.h"\nint main(void) { wmm_geometry g = {1, 8, 4, 2, 8, 0, 0, 8, 0}; wmm_operand o = {0, 32, 4, 1};\n'
+                   '  return (int)(g.window + o.stride_c) * 0 + (WMM_OK != 0) + (sizeof(wmm_geometry) != 40); }\n')
     inc = os.path.join(ROOT, "include")
     subprocess.run(["gcc", "-std=c99", "-Wall", "-Werror", "-pedantic", "-fsyntax-only", "-I", inc, str(src)], check=True)
     cxx = tmp_path / "use.cc"

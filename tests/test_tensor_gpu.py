@@ -421,3 +421,40 @@ def test_band_n_and_band_t_tf32(wm, shape):
     _assert_tf32_close(gv2, want_gv, "grad_v tf32")
     assert (ga.cpu().numpy()[:, mask] == 0).all()
     assert N.device_status() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_row_ranges_of_a_band_tensor_in_place(wm, dtype):
+    """The tensor-core kernels address a range of rows of a longer band tensor where it lies (a batch stride larger than
+    the range): what a sequence shard does when it computes its interior rows before the halo has arrived and the edge
+    strips after.  band_nt writes only the range; band_n and band_t read only the range."""
+    from window_matmul import _native as N
+
+    B, M, Nn, w = 3, 1024, 64, 128
+    flags = N.FLAG_REQUIRE_TENSOR | (N.FLAG_TF32 if dtype == torch.float32 else 0)
+    d = _inputs((B, M, Nn, w), dtype if dtype != torch.float32 else torch.float32)
+    q, kt, v, go = (H.to_dev(d[k], dtype) for k in ("q", "kt", "v", "g_out"))
+    full = wm.band_nt(q, kt, w, flags=flags)
+    band = torch.full((B, M, 2 * w + 1), float("nan"), dtype=dtype, device="cuda")
+    for r0, r1 in ((w, M - w), (0, w), (M - w, M)):          # interior first, then the two edge strips
+        wm.band_nt(q[:, r0:r1], kt, w, other_off=r0, out=band[:, r0:r1], flags=flags)
+        torch.cuda.synchronize()
+        assert torch.equal(band[:, r0:r1], full[:, r0:r1])
+        if r0 == w:
+            assert torch.isnan(band[:, :w]).all() and torch.isnan(band[:, M - w:]).all()   # nothing outside the range was touched
+    assert torch.equal(band, full)
+    o_full = wm.band_n(full, v, w, flags=flags)
+    gv_full = wm.band_t(full, go, w, flags=flags)
+    r0, r1 = 256, 640
+    o = wm.band_n(full[:, r0:r1], v, w, other_off=r0, flags=flags)
+    assert torch.equal(o, o_full[:, r0:r1])
+    part = wm.band_t(full[:, r0:r1], go[:, r0:r1], w, other_rows=M, other_off=r0, flags=flags)
+    rest = full.clone()
+    rest[:, r0:r1] = 0
+    other = wm.band_t(rest, go, w, flags=flags)
+    tol = 2e-2 if dtype == torch.bfloat16 else 2e-5
+    H.assert_lowp_close(part.float() + other.float(), gv_full.float().cpu().numpy(), "band_t over a row range", rel=tol)
+    assert N.device_status() == 0
+    # the other kernel families refuse a strided band instead of misreading it
+    with pytest.raises(RuntimeError, match="tensor-core kernels only"):
+        wm.band_nt(q[:, :64].float(), kt.float(), w, out=torch.empty(B, M, 2 * w + 1, device="cuda")[:, :64], flags=N.FLAG_FORCE_GENERIC)
