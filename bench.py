@@ -43,8 +43,8 @@ METRIC = "fwd+bwd window+unwindow us at B=96 M=4096 N=64 w=256"
 # B=48 (196608 rows per launch).
 # (bytes per band row, bytes per launch).  The window backward (one sweep over grad_A) re-reads a fixed number of boxes at
 # the start of every CTA's run: 59.7 MB per launch whatever the batch, on top of 1461.8 B per band row.
-NCU_DRAM_BYTES_PER_ROW = {"c2": {"band_nt": (1008.8, 0.0), "band_n+band_t": (1461.8, 59.7e6), "band_n": (1245.0, 0.0),
-                                 "band_t": (1242.9, 0.0)}}
+NCU_DRAM_BYTES_PER_ROW = {"c2": {"band_nt": (990.9, 0.0), "band_n+band_t": (1449.8, 59.7e6), "band_n": (1245.4, 0.0),
+                                 "band_t": (1226.9, 0.0)}}
 
 
 def algorithmic(B, M, N, w, e):

@@ -96,3 +96,49 @@ def test_dilated_windows_by_views(dtype, dilation):
 
     for name, got, ref in (("o", out, dense), ("gq", qc.grad, qd.grad), ("gk", kc.grad, kd.grad), ("gv", vc.grad, vd.grad)):
         H.assert_lowp_close(got, ref.detach().numpy(), name, rel=rel)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_global_tokens_on_top_of_the_window(dtype):
+    """Windowed attention with a few global positions (every query sees them, they see everything) against the dense
+    formulation with the same mask in float64, forward and backward."""
+    from window_matmul.global_tokens import global_window_attention
+
+    B, M, Nn, w = 2, 384, 64, 16
+    g = torch.Generator().manual_seed(11)
+    q, k, v, go = (torch.randn(B, M, Nn, generator=g).to(dtype) for _ in range(4))
+    gidx = torch.tensor([0, 5, 200, 383])
+    scale = 1.0 / math.sqrt(Nn)
+
+    qd, kd, vd = (t.double().requires_grad_(True) for t in (q, k, v))
+    i = torch.arange(M)
+    allowed = (i[None, :] - i[:, None]).abs() <= w
+    allowed[:, gidx] = True
+    allowed[gidx, :] = True
+    dense = torch.softmax((qd @ kd.transpose(-1, -2) * scale).masked_fill(~allowed, float("-inf")), -1) @ vd
+    dense.backward(go.double())
+
+    qc, kc, vc = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    out = global_window_attention(qc, kc, vc, w, gidx)
+    out.backward(go.cuda())
+    torch.cuda.synchronize()
+    import helpers as H
+
+    rel = 1e-4 if dtype == torch.float32 else 4e-2
+    for name, got, ref in (("o", out, dense), ("gq", qc.grad, qd.grad), ("gk", kc.grad, kd.grad), ("gv", vc.grad, vd.grad)):
+        H.assert_lowp_close(got, ref.detach().numpy(), name, rel=rel)
+
+
+def test_band_row_ranges_are_recognised_without_a_gpu():
+    """Which band tensors the wrappers hand over in place: dense ones and row ranges of dense ones (batch stride)."""
+    import importlib
+
+    impl = importlib.import_module("window_matmul.window_matmul")
+    full = torch.zeros(3, 40, 9)
+    assert impl._band_stride(full) == 0
+    assert impl._band_stride(full[:, 8:24]) == 40 * 9
+    assert impl._band_stride(full[1:]) == 0
+    assert impl._band_stride(full[:, :, :5]) is None and impl._band_stride(full[:, ::2]) is None
+    t, sb = impl._band_in(full[:, ::2])
+    assert sb == 0 and t.is_contiguous()
