@@ -31,7 +31,11 @@
 namespace wmm {
 namespace {
 
+// 256 threads x ~80 registers: a CTA fits on an SM beside a CTA of band_n / band_t / the sweep, not beside band_nt's (which
+// leaves 7 K registers free).  Two-warp CTAs would fit there too but take 49 us instead of 30 us for the C4 exchange at two
+// ranks and bought 3 us of overlap: not worth it.
 constexpr int kHaloThreads = 256;
+constexpr int kHaloMaxBlocks = 128;
 constexpr int kHaloMaxBuffers = 4;
 constexpr int kHaloUnroll = 4;           // independent 16-byte peer loads in flight per thread
 constexpr unsigned long long ST_HALO_TIMEOUT = 1ull << 5;
@@ -226,7 +230,7 @@ cudaError_t launch_halo_pull(const wmm_halo_buffer *bufs, int count, const wmm_h
   const long long per_side = (long long)count * batch * a.strip_vecs;
   long long blocks = (per_side + kHaloThreads * kHaloUnroll - 1) / (kHaloThreads * kHaloUnroll);
   if (blocks < 1) blocks = 1;
-  if (blocks > 128) blocks = 128;
+  if (blocks > kHaloMaxBlocks) blocks = kHaloMaxBlocks;
   switch (dtype) {
     case WMM_F16: halo_pull_kernel<__half><<<(int)blocks, kHaloThreads, 0, stream>>>(a); break;
     case WMM_BF16: halo_pull_kernel<__nv_bfloat16><<<(int)blocks, kHaloThreads, 0, stream>>>(a); break;
