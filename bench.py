@@ -755,23 +755,28 @@ def measure_seq_sharded(args, torch, impl, N_, rank, world, dev, workload, steps
     graph = None
     result = {}
     with torch.cuda.stream(stream):
-        side = torch.cuda.Stream(device=dev) if peer and args.overlap else None
+        side = torch.cuda.Stream(device=dev) if peer and args.overlap > 0 else None
 
         def overlapped_step():
-            """The exchanges on a side stream under the contractions that do not need them: the window forward of the
+            """Exchanges on a side stream under contractions that do not need them.  Level 1: the grad_V partial rows are
+            reduced under the window backward (the grad_K ones at the end).  Level 2: also the window forward of the
             interior rows (whose windows touch no margin) runs while the K^T / V margins arrive, the two edge strips
-            after; the grad_V partial rows are reduced under the window backward, the grad_K ones at the end."""
+            after."""
             lo_r, hi_r = ph.interior_rows()
             kt_ext, v_ext = ph.ext(0), ph.ext(1)
-            side.wait_stream(stream)
-            with torch.cuda.stream(side):
+            if args.overlap >= 2:
+                side.wait_stream(stream)
+                with torch.cuda.stream(side):
+                    ph.exchange()
+                    arrived = torch.cuda.Event()
+                    arrived.record(side)
+                impl.band_nt(q[:, lo_r:hi_r], kt_ext, w, other_off=off + lo_r, seq=seq, out=a[:, lo_r:hi_r])
+                stream.wait_event(arrived)
+                impl.band_nt(q[:, :lo_r], kt_ext, w, other_off=off, seq=seq, out=a[:, :lo_r])
+                impl.band_nt(q[:, hi_r:], kt_ext, w, other_off=off + hi_r, seq=seq, out=a[:, hi_r:])
+            else:
                 ph.exchange()
-                arrived = torch.cuda.Event()
-                arrived.record(side)
-            impl.band_nt(q[:, lo_r:hi_r], kt_ext, w, other_off=off + lo_r, seq=seq, out=a[:, lo_r:hi_r])
-            stream.wait_event(arrived)
-            impl.band_nt(q[:, :lo_r], kt_ext, w, other_off=off, seq=seq, out=a[:, :lo_r])
-            impl.band_nt(q[:, hi_r:], kt_ext, w, other_off=off + hi_r, seq=seq, out=a[:, hi_r:])
+                launch_list[0][1](kt_ext, v_ext)
             for _, fn in launch_list[1:4]:      # unwindow forward, grad_A, grad_V partial rows
                 fn(kt_ext, v_ext)
             gv_ready = torch.cuda.Event()
@@ -875,8 +880,9 @@ def measure_seq_sharded(args, torch, impl, N_, rank, world, dev, workload, steps
     peak, peak_kind = measured_peaks()
     result.update({
         "value_us": us, "n_gpus": world, "steps": steps, "workload": workload_name(workload), "rows_per_gpu": Ml,
-        "overlap": ("exchanges on a side stream: window forward of the interior rows under the K^T/V exchange, grad_V reduction under "
-                    "the window backward" if (peer and side is not None) else "none: exchanges in stream order"),
+        "overlap": ("none: exchanges in stream order" if not (peer and side is not None) else
+                    "grad_V reduction on a side stream under the window backward" if args.overlap == 1 else
+                    "K^T/V exchange under the window forward of the interior rows, grad_V reduction under the window backward"),
         "exchange": ("peer memory: one kernel of the library per exchange" if peer else
                      "NCCL send/recv (torch.distributed)" if world > 1 else "none"),
         "halo_bytes_per_rank_step": 0 if world == 1 else 4 * 2 * B * w * N * e,  # K^T, V margins in; grad_K, grad_V partials in
@@ -935,9 +941,9 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--blocks", type=int, default=0, help="timed blocks of --steps steps each (0: enough for about a second, at least 50)")
     ap.add_argument("--no-reference-cuda", action="store_true", help="skip the short run of the reference's CUDA kernels beside the headline")
-    ap.add_argument("--overlap", action="store_true",
-                    help="sequence-sharded step: exchanges on a side stream under the interior rows of the window forward and under the "
-                         "window backward (default: stream order; measured equal at 2 GPUs, where an exchange is 2 %% of the step)")
+    ap.add_argument("--overlap", type=int, default=1, choices=[0, 1, 2],
+                    help="sequence-sharded step: 0 = exchanges in stream order; 1 = the grad_V reduction on a side stream under the "
+                         "window backward; 2 = also the K^T/V exchange under the window forward of the interior rows")
     ap.add_argument("--no-seq-extra", action="store_true", help="on several GPUs: skip the sequence-sharded config 4 step reported beside the headline")
     ap.add_argument("--tf32", action="store_true", help="fp32 workloads: multiply on the tensor cores as tf32 (WMM_FLAG_TF32) instead of the exact-order kernels")
     ap.add_argument("--branches", type=int, default=2, choices=[1, 2], help="capture the step as one chain (1) or with its real dependencies (2)")

@@ -331,7 +331,7 @@ template <int ET, int NH, bool YMN, bool PAIRED> cudaError_t launch_nt(const Pro
 
 template <int NH> cudaError_t launch_nt_any(const Problem &p, cudaStream_t stream) {
   if (p.dtype == WMM_F32) {   // tf32 products, fp32 band
-    if constexpr (NH <= 64) return launch_nt<2, NH, false, false>(p, stream);
+    if constexpr (NH <= 64) return (p.w % 64) == 0 ? launch_nt<2, NH, false, true>(p, stream) : launch_nt<2, NH, false, false>(p, stream);
     else return cudaErrorNotSupported;
   }
   const bool bf16 = p.dtype == WMM_BF16;

@@ -97,7 +97,7 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   constexpr int ES = F32 ? 4 : 2;
   constexpr int ITEM = 128 / ES;      // positions per epilogue item = per staging box line: 64 or 32
   constexpr int IPC = CHUNK / ITEM;   // items per chunk: 2 or 4
-  static_assert(!(F32 && (PAIRED || YMN)), "the fp32 variant has neither the merged epilogue nor position-major operands");
+  static_assert(!(F32 && YMN), "the fp32 variant takes hidden-contiguous operands only");
   using S = NtSmem<NH, ES>;
   using OT = KMajorTileE<NH, ES>;
   extern __shared__ uint8_t smem_raw[];
@@ -320,6 +320,74 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           const int kl_lo = kk_lo - cl * CHUNK, kl_hi = kk_hi - cl * CHUNK;
           const bool edge_l = kl_lo > 0 || kl_hi < CHUNK;
           const bool direct_l = (rr == vr - 1);  // last valid row: its last-chunk piece has no staging line
+          if constexpr (F32) {
+            // fp32: an item is ONE 32-column block (g = h), a staging line holds its 32 values in eight 16-byte pieces
+            const uint32_t taddr_lq = tmem_base + as2 * CHUNK + h * ITEM + lane_sel;
+            float *row_lf = static_cast<float *>(p.band) + (int64_t)b * p.band_sb + (int64_t)i * W + (cl * CHUNK - rr);
+            const int g = h;
+            if (g < quarter) {
+              uint32_t vl[32];
+              tmem_ld_x32(taddr_lq, vl);
+              tmem_ld_wait();
+              if (edge_l) mask_columns(vl, g * 32, kl_lo, kl_hi);
+              if (rows_ok) {
+#pragma unroll
+                for (int q8 = 0; q8 < 8; q8++) {
+                  const uint4 pc = make_uint4(vl[4 * q8], vl[4 * q8 + 1], vl[4 * q8 + 2], vl[4 * q8 + 3]);
+                  if (!direct_l) st_shared_v4(stage_addr(stage, rr + 1, q8), pc);
+                  else *reinterpret_cast<uint4 *>(row_lf + g * 32 + q8 * 4) = pc;
+                }
+              }
+            } else if (g > quarter) {
+              uint32_t v0[32];
+              tmem_ld_x32(taddr, v0);
+              tmem_ld_wait();
+              if (edge) mask_columns(v0, g * 32, kk_lo, kk_hi);
+              if (rows_ok) {
+#pragma unroll
+                for (int q8 = 0; q8 < 8; q8++)
+                  st_shared_v4(stage_addr(stage, rr, q8), make_uint4(v0[4 * q8], v0[4 * q8 + 1], v0[4 * q8 + 2], v0[4 * q8 + 3]));
+              }
+            } else {
+              // diagonal block: line rr takes columns >= lane from this thread's first-chunk row and columns < lane from
+              // the last-chunk row of the thread one lane below; lane 31 also writes its own last-chunk row (line rr + 1)
+              uint32_t v0[32], vl[32];
+              tmem_ld_x32(taddr, v0);
+              tmem_ld_x32(taddr_lq, vl);
+              tmem_ld_wait();
+              if (edge) mask_columns(v0, g * 32, kk_lo, kk_hi);
+              if (edge_l) mask_columns(vl, g * 32, kl_lo, kl_hi);
+              uint32_t m[32];
+#pragma unroll
+              for (int k2 = 0; k2 < 32; k2++) {
+                const uint32_t up = __shfl_up_sync(0xffffffffu, vl[k2], 1);
+                m[k2] = (k2 >= lane) ? v0[k2] : up;
+              }
+              if (rows_ok) {
+#pragma unroll
+                for (int q8 = 0; q8 < 8; q8++)
+                  st_shared_v4(stage_addr(stage, rr, q8), make_uint4(m[4 * q8], m[4 * q8 + 1], m[4 * q8 + 2], m[4 * q8 + 3]));
+                if (direct_l) {
+                  // the last valid row of the tile: columns 32*quarter .. rr of its last-chunk row go straight to the band
+#pragma unroll
+                  for (int q8 = 0; q8 < 8; q8++) {
+                    const int kk0 = g * 32 + q8 * 4;
+                    if (kk0 + 3 <= rr) {
+                      *reinterpret_cast<uint4 *>(row_lf + kk0) = make_uint4(vl[4 * q8], vl[4 * q8 + 1], vl[4 * q8 + 2], vl[4 * q8 + 3]);
+                    } else if (kk0 <= rr) {
+#pragma unroll
+                      for (int e = 0; e < 4; e++)
+                        if (kk0 + e <= rr) row_lf[kk0 + e] = __uint_as_float(vl[4 * q8 + e]);
+                    }
+                  }
+                } else if (lane == 31) {
+#pragma unroll
+                  for (int q8 = 0; q8 < 8; q8++)
+                    st_shared_v4(stage_addr(stage, rr + 1, q8), make_uint4(vl[4 * q8], vl[4 * q8 + 1], vl[4 * q8 + 2], vl[4 * q8 + 3]));
+                }
+              }
+            }
+          } else {
           uint16_t *row_l = band + (int64_t)b * p.band_sb + (int64_t)i * W + (cl * CHUNK - rr);
 #pragma unroll
           for (int gb = 0; gb < 2; gb++) {
@@ -390,6 +458,7 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 }
               }
             }
+          }
           }
           tc_fence_before_sync();
           mbar_arrive(bar_acc_empty(as));
