@@ -757,39 +757,44 @@ def measure_seq_sharded(args, torch, impl, N_, rank, world, dev, workload, steps
     with torch.cuda.stream(stream):
         side = torch.cuda.Stream(device=dev) if peer and args.overlap > 0 else None
 
+        free_sms = max(0, args.overlap_sms)
+        sms_total = torch.cuda.get_device_properties(dev).multi_processor_count
+
+        def beside(exchange_fn, contraction_fn):
+            """An exchange on the side stream beside a contraction on the main one.  The contraction leaves `free_sms` SMs,
+            the exchange is capped at two CTAs for each of them (wmm_set_cta_limits): without the caps the exchange's
+            CTAs find no SM with room and run after the contraction."""
+            ready = torch.cuda.Event()
+            ready.record(stream)
+            with N_.cta_limits(sms_total - free_sms if free_sms else 0, 2 * free_sms):
+                with torch.cuda.stream(side):
+                    side.wait_event(ready)
+                    r = exchange_fn()
+                    done = torch.cuda.Event()
+                    done.record(side)
+                contraction_fn()
+            stream.wait_event(done)
+            return r
+
         def overlapped_step():
-            """Exchanges on a side stream under contractions that do not need them.  Level 1: the grad_V partial rows are
-            reduced under the window backward (the grad_K ones at the end).  Level 2: also the window forward of the
-            interior rows (whose windows touch no margin) runs while the K^T / V margins arrive, the two edge strips
-            after."""
+            """Exchanges beside contractions that do not need them.  Level 1: K^T margins first (nothing to hide them
+            under), V margins beside the window forward, the grad_V reduction beside the grad_K contraction, the grad_K
+            reduction beside the grad_Q one.  Level 2: also the K^T exchange is hidden, beside the window forward of the
+            interior rows (whose windows touch no margin); the two edge strips follow."""
             lo_r, hi_r = ph.interior_rows()
             kt_ext, v_ext = ph.ext(0), ph.ext(1)
             if args.overlap >= 2:
-                side.wait_stream(stream)
-                with torch.cuda.stream(side):
-                    ph.exchange()
-                    arrived = torch.cuda.Event()
-                    arrived.record(side)
-                impl.band_nt(q[:, lo_r:hi_r], kt_ext, w, other_off=off + lo_r, seq=seq, out=a[:, lo_r:hi_r])
-                stream.wait_event(arrived)
+                beside(lambda: ph.exchange(),
+                       lambda: impl.band_nt(q[:, lo_r:hi_r], kt_ext, w, other_off=off + lo_r, seq=seq, out=a[:, lo_r:hi_r]))
                 impl.band_nt(q[:, :lo_r], kt_ext, w, other_off=off, seq=seq, out=a[:, :lo_r])
                 impl.band_nt(q[:, hi_r:], kt_ext, w, other_off=off + hi_r, seq=seq, out=a[:, hi_r:])
             else:
-                ph.exchange()
-                launch_list[0][1](kt_ext, v_ext)
+                ph.exchange(0)
+                beside(lambda: ph.exchange(1), lambda: launch_list[0][1](kt_ext, v_ext))
             for _, fn in launch_list[1:4]:      # unwindow forward, grad_A, grad_V partial rows
                 fn(kt_ext, v_ext)
-            gv_ready = torch.cuda.Event()
-            gv_ready.record(stream)
-            with torch.cuda.stream(side):
-                side.wait_event(gv_ready)
-                gv_rows = ph.reduce(1)[0]
-                gv_done = torch.cuda.Event()
-                gv_done.record(side)
-            for _, fn in launch_list[4:]:       # window backward: grad_Q, grad_K partial rows
-                fn(kt_ext, v_ext)
-            stream.wait_event(gv_done)
-            gk_rows = ph.reduce(0)[0]
+            gv_rows = beside(lambda: ph.reduce(1)[0], lambda: launch_list[5][1](kt_ext, v_ext))   # grad_K partial rows
+            gk_rows = beside(lambda: ph.reduce(0)[0], lambda: launch_list[4][1](kt_ext, v_ext))   # grad_Q
             return [gk_rows, gv_rows]
 
         def raw_step():
@@ -881,8 +886,10 @@ def measure_seq_sharded(args, torch, impl, N_, rank, world, dev, workload, steps
     result.update({
         "value_us": us, "n_gpus": world, "steps": steps, "workload": workload_name(workload), "rows_per_gpu": Ml,
         "overlap": ("none: exchanges in stream order" if not (peer and side is not None) else
-                    "grad_V reduction on a side stream under the window backward" if args.overlap == 1 else
-                    "K^T/V exchange under the window forward of the interior rows, grad_V reduction under the window backward"),
+                    ("V exchange beside the window forward, grad_V / grad_K reductions beside the grad_K / grad_Q contractions"
+                     if args.overlap == 1 else
+                     "K^T and V exchange beside the window forward of the interior rows, reductions beside grad_K / grad_Q")
+                    + "; %d SMs left to each exchange" % max(0, args.overlap_sms)),
         "exchange": ("peer memory: one kernel of the library per exchange" if peer else
                      "NCCL send/recv (torch.distributed)" if world > 1 else "none"),
         "halo_bytes_per_rank_step": 0 if world == 1 else 4 * 2 * B * w * N * e,  # K^T, V margins in; grad_K, grad_V partials in
@@ -942,8 +949,11 @@ def main():
     ap.add_argument("--blocks", type=int, default=0, help="timed blocks of --steps steps each (0: enough for about a second, at least 50)")
     ap.add_argument("--no-reference-cuda", action="store_true", help="skip the short run of the reference's CUDA kernels beside the headline")
     ap.add_argument("--overlap", type=int, default=1, choices=[0, 1, 2],
-                    help="sequence-sharded step: 0 = exchanges in stream order; 1 = the grad_V reduction on a side stream under the "
-                         "window backward; 2 = also the K^T/V exchange under the window forward of the interior rows")
+                    help="sequence-sharded step: 0 = exchanges in stream order; 1 = the V exchange and both reductions on a side "
+                         "stream beside contractions that do not need them; 2 = also the K^T exchange, beside the window forward "
+                         "of the interior rows")
+    ap.add_argument("--overlap-sms", type=int, default=8,
+                    help="SMs a contraction leaves to the exchange that runs beside it (0: no caps)")
     ap.add_argument("--no-seq-extra", action="store_true", help="on several GPUs: skip the sequence-sharded config 4 step reported beside the headline")
     ap.add_argument("--tf32", action="store_true", help="fp32 workloads: multiply on the tensor cores as tf32 (WMM_FLAG_TF32) instead of the exact-order kernels")
     ap.add_argument("--branches", type=int, default=2, choices=[1, 2], help="capture the step as one chain (1) or with its real dependencies (2)")

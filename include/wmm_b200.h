@@ -129,6 +129,13 @@ WMM_API const char *wmm_last_error_string(void);
 WMM_API const char *wmm_status_string(int status);
 /* Number of kernels this library has launched in this process so far (all threads). */
 WMM_API uint64_t wmm_launch_count(void);
+/* Caps the grid of the launches that follow (process-wide, read when a launch is issued or captured; 0 = no cap, the
+ * default): `contraction_ctas` for the persistent tensor-core kernels (one CTA per SM otherwise), `exchange_ctas` for
+ * wmm_halo_pull / wmm_halo_pull_static (two CTAs per SM, four times the loads in flight per thread).  For a caller that
+ * runs an exchange on one stream beside a contraction on another: with, say, 140 and 16 the contraction leaves 8 SMs
+ * and the exchange runs there instead of waiting for an SM with room.  Results do not depend on the caps.  The reference
+ * has no counterpart (it runs one kernel at a time).  Negative values fail with WMM_ERR_SHAPE. */
+WMM_API int wmm_set_cta_limits(int contraction_ctas, int exchange_ctas);
 /* Reads (and, if `clear` is non-zero, resets) the status word that a kernel sets when one of its bounded
  * waits runs out.  0 = clean.  Synchronises the current device.  Returns the word, or a negative status. */
 WMM_API int64_t wmm_device_status(int clear);

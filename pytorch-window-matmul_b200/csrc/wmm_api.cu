@@ -10,6 +10,12 @@ namespace {
 
 thread_local char tls_error[512] = "no error";
 std::atomic<uint64_t> g_launches{0};
+}  // namespace
+namespace wmm {
+std::atomic<int> g_contraction_cta_limit{0};
+std::atomic<int> g_exchange_cta_limit{0};
+}  // namespace wmm
+namespace {
 
 int fail(int status, const char *fmt, ...) {
   va_list ap;
@@ -294,6 +300,14 @@ int wmm_halo_pull_static(const wmm_halo_buffer *buffers, int count, const wmm_ha
 }
 
 uint64_t wmm_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int wmm_set_cta_limits(int contraction_ctas, int exchange_ctas) {
+  if (contraction_ctas < 0 || exchange_ctas < 0)
+    return fail(WMM_ERR_SHAPE, "CTA limits must be >= 0 (0 = no limit), got %d and %d", contraction_ctas, exchange_ctas);
+  wmm::g_contraction_cta_limit.store(contraction_ctas, std::memory_order_relaxed);
+  wmm::g_exchange_cta_limit.store(exchange_ctas, std::memory_order_relaxed);
+  return WMM_OK;
+}
 
 int64_t wmm_device_status(int clear) {
   unsigned long long word = 0;

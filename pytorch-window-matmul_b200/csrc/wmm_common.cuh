@@ -3,6 +3,7 @@
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <atomic>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -60,6 +61,11 @@ cudaError_t launch_halo_pull(const wmm_halo_buffer *bufs, int count, const wmm_h
 cudaError_t launch_halo_pull_static(const wmm_halo_buffer *bufs, int count, const wmm_halo_flags &flags, int lane, int batch,
                                     int rows, int cols, int window, int dtype, bool accumulate, cudaStream_t stream,
                                     int *launches);
+
+// Process-wide caps on the grid of the persistent tensor-core contractions and of the halo exchange (0 = none), set by
+// wmm_set_cta_limits and read at launch time: a caller that runs an exchange beside a contraction gives each its SMs.
+extern std::atomic<int> g_contraction_cta_limit;
+extern std::atomic<int> g_exchange_cta_limit;
 
 // Launchers describe a failure (which step, which driver code) here; the API layer appends it to the
 // error string of the calling thread.

@@ -31,13 +31,16 @@
 namespace wmm {
 namespace {
 
-// 256 threads x ~80 registers: a CTA fits on an SM beside a CTA of band_n / band_t / the sweep, not beside band_nt's (which
-// leaves 7 K registers free).  Two-warp CTAs would fit there too but take 49 us instead of 30 us for the C4 exchange at two
-// ranks and bought 3 us of overlap: not worth it.
+// 256 threads per CTA.  A CTA does not fit on an SM beside a CTA of the tensor-core contractions (those take nearly all of
+// an SM's shared memory, band_nt nearly all registers too; two-warp CTAs would fit beside band_nt but take 49 us instead of
+// 30 us for the C4 exchange at two ranks and bought 3 us).  An exchange that should run beside a contraction gets SMs of its
+// own instead: wmm_set_cta_limits caps the contraction's grid and this kernel's, which then keeps 16 loads in flight per
+// thread on two CTAs per SM.
 constexpr int kHaloThreads = 256;
 constexpr int kHaloMaxBlocks = 128;
 constexpr int kHaloMaxBuffers = 4;
 constexpr int kHaloUnroll = 4;           // independent 16-byte peer loads in flight per thread
+constexpr int kHaloUnrollFew = 16;       // ... when a CTA limit leaves the exchange a few SMs only
 constexpr unsigned long long ST_HALO_TIMEOUT = 1ull << 5;
 constexpr unsigned long long kReadyWaitNs = 1000ull * 1000ull * 1000ull;
 constexpr unsigned long long kGoWaitNs = 1500ull * 1000ull * 1000ull;     // local wait for CTA 0's verdict
@@ -113,8 +116,8 @@ template <typename T> __device__ __forceinline__ uint4 add16(uint4 a, uint4 b) {
   return a;
 }
 
-template <typename T>
-__global__ void __launch_bounds__(kHaloThreads) halo_pull_kernel(const HaloArgs a) {
+template <typename T, int UNROLL>
+__global__ void __launch_bounds__(kHaloThreads, UNROLL > 4 ? 2 : 1) halo_pull_kernel(const HaloArgs a) {
   __shared__ int ok_s[2];
   __shared__ int last_s;
   const unsigned e = *reinterpret_cast<volatile unsigned *>(a.epoch_word) + 1u;
@@ -138,42 +141,51 @@ __global__ void __launch_bounds__(kHaloThreads) halo_pull_kernel(const HaloArgs 
   }
   __syncthreads();
 
-  // work items of one side: (buffer, batch entry, vector of the strip); kHaloUnroll of them in flight per thread
+  // work items of one side: (buffer, batch entry, vector of the strip); UNROLL of them in flight per thread
   const long long per_buf = (long long)a.batch * a.strip_vecs;
   const long long per_side = (long long)a.count * per_buf;
   for (int side = 0; side < 2; ++side) {
     if (!ok_s[side]) continue;
-    for (long long it0 = (long long)blockIdx.x * (kHaloThreads * kHaloUnroll) + threadIdx.x; it0 < per_side;
-         it0 += (long long)gridDim.x * (kHaloThreads * kHaloUnroll)) {
-      uint4 val[kHaloUnroll], own[kHaloUnroll];
-      uint4 *dst[kHaloUnroll];
+    // where item `it` comes from (in the neighbour's buffer) and goes to (in mine)
+    auto place = [&](long long it, const uint4 *&src, uint4 *&dst) {
+      const int t = (int)(it / per_buf);
+      const long long q = it % per_buf;
+      const long long b = q / a.strip_vecs, v = q % a.strip_vecs;
+      long long s_off, d_off;
+      if (!a.accumulate) {
+        // lower: neighbour's last w own rows (they end where its upper margin starts) -> my lower margin
+        // upper: neighbour's first w own rows (they start after its lower margin)     -> my upper margin
+        s_off = b * a.row_vecs + (side == 0 ? a.own_vecs - a.strip_vecs : a.strip_vecs) + v;
+        d_off = b * a.row_vecs + (side == 0 ? 0 : a.own_vecs) + v;
+      } else {
+        // lower: neighbour's upper margin -> added to my first w own rows; upper: neighbour's lower margin -> my last w
+        s_off = b * a.row_vecs + (side == 0 ? a.own_vecs : 0) + v;
+        d_off = b * a.row_vecs + (side == 0 ? a.strip_vecs : a.own_vecs - a.strip_vecs) + v;
+      }
+      src = static_cast<const uint4 *>(side == 0 ? a.lower[t] : a.upper[t]) + s_off;
+      dst = static_cast<uint4 *>(a.local[t]) + d_off;
+    };
+    for (long long it0 = (long long)blockIdx.x * (kHaloThreads * UNROLL) + threadIdx.x; it0 < per_side;
+         it0 += (long long)gridDim.x * (kHaloThreads * UNROLL)) {
+      uint4 val[UNROLL];
 #pragma unroll
-      for (int u = 0; u < kHaloUnroll; ++u) {
+      for (int u = 0; u < UNROLL; ++u) {
         const long long it = it0 + (long long)u * kHaloThreads;
-        dst[u] = nullptr;
         if (it >= per_side) continue;
-        const int t = (int)(it / per_buf);
-        const long long q = it % per_buf;
-        const long long b = q / a.strip_vecs, v = q % a.strip_vecs;
-        const uint4 *src = static_cast<const uint4 *>(side == 0 ? a.lower[t] : a.upper[t]);
-        long long s_off, d_off;
-        if (!a.accumulate) {
-          // lower: neighbour's last w own rows (they end where its upper margin starts) -> my lower margin
-          // upper: neighbour's first w own rows (they start after its lower margin)     -> my upper margin
-          s_off = b * a.row_vecs + (side == 0 ? a.own_vecs - a.strip_vecs : a.strip_vecs) + v;
-          d_off = b * a.row_vecs + (side == 0 ? 0 : a.own_vecs) + v;
-        } else {
-          // lower: neighbour's upper margin -> added to my first w own rows; upper: neighbour's lower margin -> my last w
-          s_off = b * a.row_vecs + (side == 0 ? a.own_vecs : 0) + v;
-          d_off = b * a.row_vecs + (side == 0 ? a.strip_vecs : a.own_vecs - a.strip_vecs) + v;
-        }
-        dst[u] = static_cast<uint4 *>(a.local[t]) + d_off;
-        val[u] = __ldcg(src + s_off);
-        if (a.accumulate) own[u] = *dst[u];
+        const uint4 *src;
+        uint4 *dst;
+        place(it, src, dst);
+        val[u] = __ldcg(src);
       }
 #pragma unroll
-      for (int u = 0; u < kHaloUnroll; ++u)
-        if (dst[u]) *dst[u] = a.accumulate ? add16<T>(own[u], val[u]) : val[u];
+      for (int u = 0; u < UNROLL; ++u) {
+        const long long it = it0 + (long long)u * kHaloThreads;
+        if (it >= per_side) continue;
+        const uint4 *src;
+        uint4 *dst;
+        place(it, src, dst);
+        *dst = a.accumulate ? add16<T>(*dst, val[u]) : val[u];
+      }
     }
   }
   __syncthreads();
@@ -228,15 +240,28 @@ cudaError_t launch_halo_pull(const wmm_halo_buffer *bufs, int count, const wmm_h
   a.scratch = scratch;
   a.status = device_status_word();
   const long long per_side = (long long)count * batch * a.strip_vecs;
-  long long blocks = (per_side + kHaloThreads * kHaloUnroll - 1) / (kHaloThreads * kHaloUnroll);
+  // With a CTA limit the exchange runs beside a contraction on the few SMs that one leaves free: fewer CTAs (two per SM),
+  // each with four times the loads in flight.
+  const int cap = g_exchange_cta_limit.load(std::memory_order_relaxed);
+  const int unroll = cap > 0 ? kHaloUnrollFew : kHaloUnroll;
+  long long blocks = (per_side + kHaloThreads * unroll - 1) / (kHaloThreads * unroll);
   if (blocks < 1) blocks = 1;
   if (blocks > kHaloMaxBlocks) blocks = kHaloMaxBlocks;
+  if (cap > 0 && blocks > cap) blocks = cap;
+#define WMM_HALO_LAUNCH(T)                                                                   \
+  do {                                                                                       \
+    if (cap > 0)                                                                             \
+      halo_pull_kernel<T, kHaloUnrollFew><<<(int)blocks, kHaloThreads, 0, stream>>>(a);      \
+    else                                                                                     \
+      halo_pull_kernel<T, kHaloUnroll><<<(int)blocks, kHaloThreads, 0, stream>>>(a);         \
+  } while (0)
   switch (dtype) {
-    case WMM_F16: halo_pull_kernel<__half><<<(int)blocks, kHaloThreads, 0, stream>>>(a); break;
-    case WMM_BF16: halo_pull_kernel<__nv_bfloat16><<<(int)blocks, kHaloThreads, 0, stream>>>(a); break;
-    case WMM_F32: halo_pull_kernel<float><<<(int)blocks, kHaloThreads, 0, stream>>>(a); break;
-    default: halo_pull_kernel<double><<<(int)blocks, kHaloThreads, 0, stream>>>(a); break;
+    case WMM_F16: WMM_HALO_LAUNCH(__half); break;
+    case WMM_BF16: WMM_HALO_LAUNCH(__nv_bfloat16); break;
+    case WMM_F32: WMM_HALO_LAUNCH(float); break;
+    default: WMM_HALO_LAUNCH(double); break;
   }
+#undef WMM_HALO_LAUNCH
   cudaError_t err = cudaGetLastError();
   if (err == cudaSuccess && launches) ++*launches;
   return err;

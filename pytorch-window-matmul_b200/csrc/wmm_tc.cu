@@ -192,7 +192,9 @@ int sm_count() {
 // so the SMs that run out of work early leave their share of the bandwidth to the others; launching fewer,
 // evenly loaded CTAs measured slower.
 int persistent_grid(int items) {
-  const int sms = sm_count();
+  int sms = sm_count();
+  const int cap = g_contraction_cta_limit.load(std::memory_order_relaxed);   // SMs left to a concurrent exchange
+  if (cap > 0 && cap < sms) sms = cap;
   return items < sms ? items : sms;
 }
 
@@ -211,7 +213,9 @@ cudaError_t launch_pdl(void (*kern)(KArgs...), int grid, int block, size_t smem,
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   static const bool no_pdl = getenv("WMM_NO_PDL") != nullptr;
-  cfg.numAttrs = no_pdl ? 0 : 1;
+  // Under a CTA limit the free SMs belong to a kernel of another stream: an early-scheduled successor would sit on them
+  // at its griddepcontrol.wait, so such launches keep plain stream order.
+  cfg.numAttrs = no_pdl || g_contraction_cta_limit.load(std::memory_order_relaxed) > 0 ? 0 : 1;
   return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
 }
 

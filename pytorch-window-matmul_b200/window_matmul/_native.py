@@ -75,6 +75,8 @@ def _load():
     lib.wmm_status_string.argtypes = [i32]
     lib.wmm_launch_count.restype = ctypes.c_uint64
     lib.wmm_launch_count.argtypes = []
+    lib.wmm_set_cta_limits.restype = i32
+    lib.wmm_set_cta_limits.argtypes = [i32, i32]
     lib.wmm_device_status.restype = ctypes.c_int64
     lib.wmm_device_status.argtypes = [i32]
     lib.wmm_query_path.restype = i32
@@ -139,6 +141,22 @@ def check(status: int) -> None:
 
 def launch_count() -> int:
     return int(lib.wmm_launch_count())
+
+
+class cta_limits:
+    """`with cta_limits(140, 16): ...` caps the grids of the contractions / exchanges launched (or captured) inside the
+    block (wmm_set_cta_limits) and lifts the caps afterwards.  Process-wide: not for threads that launch concurrently."""
+
+    def __init__(self, contraction_ctas: int = 0, exchange_ctas: int = 0):
+        self.c, self.x = int(contraction_ctas), int(exchange_ctas)
+
+    def __enter__(self):
+        check(lib.wmm_set_cta_limits(self.c, self.x))
+        return self
+
+    def __exit__(self, *exc):
+        lib.wmm_set_cta_limits(0, 0)
+        return False
 
 
 def device_status(clear: bool = True) -> int:

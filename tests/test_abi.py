@@ -31,6 +31,16 @@ def test_library_exports_every_declared_symbol():
     assert lib.wmm_version() == 3
 
 
+def test_cta_limits_are_validated_and_reset():
+    from window_matmul import _native as N
+
+    assert N.lib.wmm_set_cta_limits(-1, 0) == -2 and b">= 0" in N.lib.wmm_last_error_string()
+    assert N.lib.wmm_set_cta_limits(0, -3) == -2
+    with N.cta_limits(140, 16):
+        pass
+    assert N.lib.wmm_set_cta_limits(0, 0) == 0
+
+
 def test_argument_validation_needs_no_gpu():
     from window_matmul import _native as N
 

@@ -234,6 +234,37 @@ def test_halo_pull_serves_the_live_side_when_the_other_neighbour_is_absent():
     assert int(counters[0]) == 1 and int(counters[1]) == 0
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("accumulate", [0, 1])
+def test_exchange_under_a_cta_limit_moves_the_same_bytes(accumulate):
+    """wmm_set_cta_limits picks another grid and another unrolling of the exchange kernel, nothing else.  ONE GPU, the rank
+    as its own two neighbours (an exchange then wraps the sequence around)."""
+    import ctypes as C
+
+    sys.path[:0] = [ROOT, os.path.join(ROOT, "pytorch-window-matmul_b200")]
+    from window_matmul import _native as N
+
+    dev = torch.device("cuda", 0)
+    B, Ml, Nn, w = 5, 640, 128, 96          # 5 x 96 x 128 x 2 B per side: more than one sweep of a capped grid
+    ext = Ml + 2 * w
+    start = torch.randn(B, ext, Nn, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16)
+    stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    results = []
+    for limit in (0, 3):
+        buf = start.to(dev).clone()
+        fl = torch.zeros(4, dtype=torch.int32, device=dev)
+        counters = torch.zeros(4, dtype=torch.int32, device=dev)
+        arr = (N.HaloBuffer * 1)(N.HaloBuffer(buf.data_ptr(), buf.data_ptr(), buf.data_ptr()))
+        flags = N.HaloFlags(fl.data_ptr(), fl.data_ptr(), fl.data_ptr(), counters.data_ptr())
+        with N.cta_limits(0, limit):
+            N.check(N.lib.wmm_halo_pull(arr, 1, C.byref(flags), B, Ml, Nn, w, N.BF16, accumulate, stream))
+        torch.cuda.synchronize()
+        assert N.device_status() == 0 and int(fl[0]) == 1
+        results.append(buf.clone())
+    assert torch.equal(results[0], results[1])
+    assert not torch.equal(results[0].cpu(), start)
+
+
 def _peer_chain_worker(rank, world, port, shape, dtype_name, out_dir):
     import importlib
 

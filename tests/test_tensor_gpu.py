@@ -458,3 +458,31 @@ def test_row_ranges_of_a_band_tensor_in_place(wm, dtype):
     # the other kernel families refuse a strided band instead of misreading it
     with pytest.raises(RuntimeError, match="tensor-core kernels only"):
         wm.band_nt(q[:, :64].float(), kt.float(), w, out=torch.empty(B, M, 2 * w + 1, device="cuda")[:, :64], flags=N.FLAG_FORCE_GENERIC)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_results_do_not_depend_on_a_cta_limit(wm, dtype):
+    """wmm_set_cta_limits gives the persistent kernels a smaller grid (SMs left to an exchange on another stream); the
+    tiles are the same and so is every output bit, window backward in one launch included."""
+    from window_matmul import _native as N
+
+    B, M, Nn, w = 6, 2048, 64, 128            # 96 row tiles: more than one per CTA at 37 CTAs
+    flags = N.FLAG_REQUIRE_TENSOR | (N.FLAG_TF32 if dtype == torch.float32 else 0)
+    d = _inputs((B, M, Nn, w), torch.float32)
+    q, kt, v, go = (H.to_dev(d[k], dtype) for k in ("q", "kt", "v", "g_out"))
+
+    def run():
+        band = wm.band_nt(q, kt, w, flags=flags)
+        out = [band, wm.band_n(band, v, w, flags=flags), wm.band_t(band, go, w, flags=flags)]
+        if dtype == torch.bfloat16:          # both halves of the window backward in one launch
+            out += list(wm.window_matmul_backward(q, kt.transpose(-1, -2), w, band))
+        torch.cuda.synchronize()
+        return out
+
+    free = run()
+    with N.cta_limits(37, 0):
+        capped = run()
+    again = run()
+    for a, b, c in zip(free, capped, again):
+        assert torch.equal(a, b) and torch.equal(a, c)
+    assert N.device_status() == 0
