@@ -762,11 +762,11 @@ def measure_seq_sharded(args, torch, impl, N_, rank, world, dev, workload, steps
 
         def beside(exchange_fn, contraction_fn):
             """An exchange on the side stream beside a contraction on the main one.  The contraction leaves `free_sms` SMs,
-            the exchange is capped at two CTAs for each of them (wmm_set_cta_limits): without the caps the exchange's
+            the exchange is capped at one CTA for each of them (wmm_set_cta_limits): without the caps the exchange's
             CTAs find no SM with room and run after the contraction."""
             ready = torch.cuda.Event()
             ready.record(stream)
-            with N_.cta_limits(sms_total - free_sms if free_sms else 0, 2 * free_sms):
+            with N_.cta_limits(sms_total - free_sms if free_sms else 0, free_sms):
                 with torch.cuda.stream(side):
                     side.wait_event(ready)
                     r = exchange_fn()

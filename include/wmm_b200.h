@@ -131,9 +131,9 @@ WMM_API const char *wmm_status_string(int status);
 WMM_API uint64_t wmm_launch_count(void);
 /* Caps the grid of the launches that follow (process-wide, read when a launch is issued or captured; 0 = no cap, the
  * default): `contraction_ctas` for the persistent tensor-core kernels (one CTA per SM otherwise), `exchange_ctas` for
- * wmm_halo_pull / wmm_halo_pull_static (two CTAs per SM, four times the loads in flight per thread).  For a caller that
- * runs an exchange on one stream beside a contraction on another: with, say, 140 and 16 the contraction leaves 8 SMs
- * and the exchange runs there instead of waiting for an SM with room.  Results do not depend on the caps.  The reference
+ * wmm_halo_pull / wmm_halo_pull_static (then one CTA per SM, large enough to keep the SM to itself, with eight times the
+ * loads in flight).  For a caller that runs an exchange on one stream beside a contraction on another: with, say, 140 and
+ * 8 on a 148-SM device the contraction leaves 8 SMs and the exchange runs there instead of waiting for an SM with room.  Results do not depend on the caps.  The reference
  * has no counterpart (it runs one kernel at a time).  Negative values fail with WMM_ERR_SHAPE. */
 WMM_API int wmm_set_cta_limits(int contraction_ctas, int exchange_ctas);
 /* Reads (and, if `clear` is non-zero, resets) the status word that a kernel sets when one of its bounded

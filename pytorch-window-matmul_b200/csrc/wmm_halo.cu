@@ -34,13 +34,14 @@ namespace {
 // 256 threads per CTA.  A CTA does not fit on an SM beside a CTA of the tensor-core contractions (those take nearly all of
 // an SM's shared memory, band_nt nearly all registers too; two-warp CTAs would fit beside band_nt but take 49 us instead of
 // 30 us for the C4 exchange at two ranks and bought 3 us).  An exchange that should run beside a contraction gets SMs of its
-// own instead: wmm_set_cta_limits caps the contraction's grid and this kernel's, which then keeps 16 loads in flight per
-// thread on two CTAs per SM.
+// own instead: wmm_set_cta_limits caps the contraction's grid and this kernel's, which then runs one 512-thread CTA per SM
+// with 16 loads in flight per thread.
 constexpr int kHaloThreads = 256;
 constexpr int kHaloMaxBlocks = 128;
 constexpr int kHaloMaxBuffers = 4;
 constexpr int kHaloUnroll = 4;           // independent 16-byte peer loads in flight per thread
 constexpr int kHaloUnrollFew = 16;       // ... when a CTA limit leaves the exchange a few SMs only
+constexpr int kHaloThreadsFew = 512;     // ... in CTAs that take an SM's whole register file (512 x ~126 registers)
 constexpr unsigned long long ST_HALO_TIMEOUT = 1ull << 5;
 constexpr unsigned long long kReadyWaitNs = 1000ull * 1000ull * 1000ull;
 constexpr unsigned long long kGoWaitNs = 1500ull * 1000ull * 1000ull;     // local wait for CTA 0's verdict
@@ -116,8 +117,8 @@ template <typename T> __device__ __forceinline__ uint4 add16(uint4 a, uint4 b) {
   return a;
 }
 
-template <typename T, int UNROLL>
-__global__ void __launch_bounds__(kHaloThreads, UNROLL > 4 ? 2 : 1) halo_pull_kernel(const HaloArgs a) {
+template <typename T, int UNROLL, int THREADS>
+__global__ void __launch_bounds__(THREADS, 1) halo_pull_kernel(const HaloArgs a) {
   __shared__ int ok_s[2];
   __shared__ int last_s;
   const unsigned e = *reinterpret_cast<volatile unsigned *>(a.epoch_word) + 1u;
@@ -165,12 +166,12 @@ __global__ void __launch_bounds__(kHaloThreads, UNROLL > 4 ? 2 : 1) halo_pull_ke
       src = static_cast<const uint4 *>(side == 0 ? a.lower[t] : a.upper[t]) + s_off;
       dst = static_cast<uint4 *>(a.local[t]) + d_off;
     };
-    for (long long it0 = (long long)blockIdx.x * (kHaloThreads * UNROLL) + threadIdx.x; it0 < per_side;
-         it0 += (long long)gridDim.x * (kHaloThreads * UNROLL)) {
+    for (long long it0 = (long long)blockIdx.x * (THREADS * UNROLL) + threadIdx.x; it0 < per_side;
+         it0 += (long long)gridDim.x * (THREADS * UNROLL)) {
       uint4 val[UNROLL];
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {
-        const long long it = it0 + (long long)u * kHaloThreads;
+        const long long it = it0 + (long long)u * THREADS;
         if (it >= per_side) continue;
         const uint4 *src;
         uint4 *dst;
@@ -179,7 +180,7 @@ __global__ void __launch_bounds__(kHaloThreads, UNROLL > 4 ? 2 : 1) halo_pull_ke
       }
 #pragma unroll
       for (int u = 0; u < UNROLL; ++u) {
-        const long long it = it0 + (long long)u * kHaloThreads;
+        const long long it = it0 + (long long)u * THREADS;
         if (it >= per_side) continue;
         const uint4 *src;
         uint4 *dst;
@@ -240,20 +241,21 @@ cudaError_t launch_halo_pull(const wmm_halo_buffer *bufs, int count, const wmm_h
   a.scratch = scratch;
   a.status = device_status_word();
   const long long per_side = (long long)count * batch * a.strip_vecs;
-  // With a CTA limit the exchange runs beside a contraction on the few SMs that one leaves free: fewer CTAs (two per SM),
-  // each with four times the loads in flight.
+  // With a CTA limit the exchange runs beside a contraction on the few SMs that one leaves free: one CTA per SM, sized
+  // (threads x registers) so that nothing else fits on its SM whichever kernel the hardware places first, with eight times
+  // the loads in flight per CTA.
   const int cap = g_exchange_cta_limit.load(std::memory_order_relaxed);
-  const int unroll = cap > 0 ? kHaloUnrollFew : kHaloUnroll;
-  long long blocks = (per_side + kHaloThreads * unroll - 1) / (kHaloThreads * unroll);
+  const long long per_cta = cap > 0 ? (long long)kHaloThreadsFew * kHaloUnrollFew : (long long)kHaloThreads * kHaloUnroll;
+  long long blocks = (per_side + per_cta - 1) / per_cta;
   if (blocks < 1) blocks = 1;
   if (blocks > kHaloMaxBlocks) blocks = kHaloMaxBlocks;
   if (cap > 0 && blocks > cap) blocks = cap;
 #define WMM_HALO_LAUNCH(T)                                                                   \
   do {                                                                                       \
     if (cap > 0)                                                                             \
-      halo_pull_kernel<T, kHaloUnrollFew><<<(int)blocks, kHaloThreads, 0, stream>>>(a);      \
+      halo_pull_kernel<T, kHaloUnrollFew, kHaloThreadsFew><<<(int)blocks, kHaloThreadsFew, 0, stream>>>(a); \
     else                                                                                     \
-      halo_pull_kernel<T, kHaloUnroll><<<(int)blocks, kHaloThreads, 0, stream>>>(a);         \
+      halo_pull_kernel<T, kHaloUnroll, kHaloThreads><<<(int)blocks, kHaloThreads, 0, stream>>>(a); \
   } while (0)
   switch (dtype) {
     case WMM_F16: WMM_HALO_LAUNCH(__half); break;

@@ -279,7 +279,9 @@ band_nt_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       // A group visits only its own items: the loop body is large, and an iteration that merely skips an item still
       // costs two jumps across it.
       const int tile_iit = iit;   // items of earlier tiles
+      if (threadIdx.x == 64 && tl == 0) WMM_TRACE_POINT(18);   // (18 -> 19 is 3.4 us in the first tile of a launch, 0.2 us later)
       for (int hitem = (grp - tile_iit - rot) & (EPI_GROUPS - 1); hitem < items_per_tile; hitem += EPI_GROUPS) {
+        if (threadIdx.x == 64 && iit == 0) WMM_TRACE_POINT(19);
         const int item = hitem / IPC, h = hitem % IPC;
         const bool pair_item = paired && item == 0;
         // stage of this item's chunk: with pairing the tile's stages hold chunks 0, last, 1, 2, ... in this order
