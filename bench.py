@@ -948,10 +948,10 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--blocks", type=int, default=0, help="timed blocks of --steps steps each (0: enough for about a second, at least 50)")
     ap.add_argument("--no-reference-cuda", action="store_true", help="skip the short run of the reference's CUDA kernels beside the headline")
-    ap.add_argument("--overlap", type=int, default=1, choices=[0, 1, 2],
-                    help="sequence-sharded step: 0 = exchanges in stream order; 1 = the V exchange and both reductions on a side "
-                         "stream beside contractions that do not need them; 2 = also the K^T exchange, beside the window forward "
-                         "of the interior rows")
+    ap.add_argument("--overlap", type=int, default=0, choices=[0, 1, 2],
+                    help="sequence-sharded step: 0 = exchanges in stream order (default: fastest measured); 1 = the V exchange "
+                         "and both reductions on a side stream beside contractions that do not need them; 2 = also the K^T "
+                         "exchange, beside the window forward of the interior rows")
     ap.add_argument("--overlap-sms", type=int, default=8,
                     help="SMs a contraction leaves to the exchange that runs beside it (0: no caps)")
     ap.add_argument("--no-seq-extra", action="store_true", help="on several GPUs: skip the sequence-sharded config 4 step reported beside the headline")
