@@ -39,6 +39,10 @@
  * reduction index, fused multiply-add by default, which is the order of the reference's kernels
  * (window_matmul_cuda.cu:24-35,64-83); WMM_FLAG_SPLIT_ROUNDING rounds product and sum separately, which
  * reproduces the reference's CPU loops (cpu/window_matmul_cpu.cpp:43,92-93,137,186-187) bit for bit.
+ * Both statements hold for FINITE inputs: band elements that do not exist (outside the band of a dense tile, outside
+ * the sequence) enter the chains as zero terms, so an Inf or NaN in an operand row reaches every output row whose
+ * tile covers it (0 * Inf), where the reference's loops touch only rows within `window`, and a sum of -0.0 comes
+ * out as +0.0.
  */
 #ifndef WMM_B200_H
 #define WMM_B200_H

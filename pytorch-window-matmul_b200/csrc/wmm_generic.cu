@@ -16,7 +16,8 @@
 //   band_n   C(i, h) = sum_p Band[i, p-off-i+w] Y[p,h]
 //   band_t   C(p, h) = sum_i Band[i, p-off-i+w] X[i,h]
 // Entries of the dense operand that fall outside the band or outside the sequence are read as zeros;
-// a zero term leaves a floating-point sum unchanged, so the chain equals the reference's shorter one.
+// with finite operands a zero term leaves a floating-point sum unchanged (up to the sign of a zero sum), so the
+// chain equals the reference's shorter one.  A non-finite operand row reaches every row of its tile (0 * Inf).
 #include "wmm_common.cuh"
 
 namespace wmm {
