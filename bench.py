@@ -341,6 +341,17 @@ def run_ours(args, torch):
         for fn in ops:
             fn()
 
+    # SMs per kernel of the DAG: [window fwd, grad_A, unwindow fwd, grad_V, window bwd]; 0 = all of them
+    sms_total = torch.cuda.get_device_properties(dev).multi_processor_count
+    tiles_per_sm = Bl * ((M + 127) // 128) / float(sms_total)
+    if args.sm_split == "auto":
+        split_on = args.branches == 2 and 0 < tiles_per_sm < 16.0
+        caps = [sms_total // 2, sms_total // 2, sms_total // 4, sms_total // 4, sms_total // 2] if split_on else [0] * 5
+    elif args.sm_split == "off":
+        caps = [0] * 5
+    else:
+        caps = [int(x) for x in args.sm_split.split(",")]
+        assert len(caps) == 5, "--sm-split takes five CTA caps"
     stream = torch.cuda.Stream(device=dev)
     with torch.cuda.stream(stream):
         for _ in range(max(3, args.warmup)):
@@ -355,16 +366,25 @@ def run_ours(args, torch):
                     # read A); grad_A needs only the upstream gradient and feeds the window backward.  Captured
                     # with its real dependencies, the tail of one kernel (SMs running out of tiles) is filled
                     # by another branch's kernel.
+                    # With few tiles per SM (a batch shard of a multi-GPU run) the fixed cost of a launch -- first loads,
+                    # the epilogue's first pass, the last wave -- is paid five times in a row, because every kernel asks
+                    # for all SMs and so runs alone.  `caps` gives the kernels of one level of the DAG a share of the
+                    # SMs each (wmm_set_cta_limits, read at capture), so they start together and pay it side by side.
                     s1, s2 = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+
+                    def capped(cap, fn):
+                        with N_.cta_limits(cap, 0):
+                            fn()
+
                     s1.wait_stream(stream)
                     with torch.cuda.stream(s1):
-                        impl.band_nt(god, vd, w, out=ga)
-                        ops[3]()
-                    ops[0]()
+                        capped(caps[1], lambda: impl.band_nt(god, vd, w, out=ga))
+                        capped(caps[4], ops[3])
+                    capped(caps[0], ops[0])
                     s2.wait_stream(stream)
                     with torch.cuda.stream(s2):
-                        impl.band_t(a, god, w, out=gv)
-                    ops[1]()
+                        capped(caps[3], lambda: impl.band_t(a, god, w, out=gv))
+                    capped(caps[2], ops[1])
                     stream.wait_stream(s1)
                     stream.wait_stream(s2)
                 else:
@@ -577,7 +597,7 @@ def run_ours(args, torch):
             if per_row:  # captured at B=48; traffic grows in proportion to the band rows of a launch
                 traffic = per_row[0] * Bl * M + per_row[1]
         line = {
-            "metric": METRIC if args.workload == "c2" and not args.batch else "fwd+bwd window+unwindow us (%s)" % args.workload,
+            "metric": METRIC if args.workload == "c2" and not args.batch and not args.rows else "fwd+bwd window+unwindow us (%s)" % args.workload,
             "value": us_per_step, "unit": "us", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
             "blocks": {"n": blocks, "steps_each": args.steps, "value_is": "median block, max over ranks",
                        "min_us": round(block_min_ms * 1e3 / args.steps, 2), "median_us": round(us_per_step, 2),
@@ -588,7 +608,7 @@ def run_ours(args, torch):
             "config": {
                 "workload": workload_name(args.workload), "batch_per_gpu": per,
                 "l2": "no flush: one step touches %.0f MB per GPU, larger than the 126 MB L2" % (total_bytes / world / 1e6),
-                "launch": ("cuda graph of %d kernels, %s" % (launches_per_step, "dependency DAG" if args.branches == 2 else "one chain")) if graph is not None else "%d stream launches" % launches_per_step,
+                "launch": ("cuda graph of %d kernels, %s" % (launches_per_step, ("dependency DAG" + (", CTAs per kernel %s" % caps if any(caps) else "")) if args.branches == 2 else "one chain")) if graph is not None else "%d stream launches" % launches_per_step,
                 "k_layout": "contiguous (B,N,M)" if args.k_layout == "bnm" else "transposed view of (B,M,N)",
                 **({"fp32_mode": "tf32 products on the tensor cores (WMM_FLAG_TF32)" if args.tf32 else "exact-order fp32"} if dt == "fp32" else {}),
             },
@@ -759,6 +779,9 @@ def measure_seq_sharded(args, torch, impl, N_, rank, world, dev, workload, steps
 
         free_sms = max(0, args.overlap_sms)
         sms_total = torch.cuda.get_device_properties(dev).multi_processor_count
+        seq_tiles_per_sm = B * ((Ml + 127) // 128) / float(sms_total)
+        seq_split = peer and not args.no_graph and args.overlap == 0 and (
+            args.sm_split != "off" and (args.sm_split != "auto" or seq_tiles_per_sm < 16.0))
 
         def beside(exchange_fn, contraction_fn):
             """An exchange on the side stream beside a contraction on the main one.  The contraction leaves `free_sms` SMs,
@@ -802,7 +825,32 @@ def measure_seq_sharded(args, torch, impl, N_, rank, world, dev, workload, steps
                 return overlapped_step()
             if peer:
                 kt_ext, v_ext = ph.exchange()
-                contractions(kt_ext, v_ext)
+                if seq_split:
+                    # The six contractions as their DAG, the kernels of a level side by side on a share of the SMs each
+                    # (a rank of an 8-GPU run has 7 row tiles per SM: the fixed cost of a launch counts):
+                    #   level 1: window forward | grad_A          (half of the SMs each)
+                    #   level 2: unwindow forward, grad_V | grad_Q, grad_K   (a quarter each)
+                    la, lb, lc = (torch.cuda.Stream(device=dev) for _ in range(3))
+                    half, quarter = sms_total // 2, sms_total // 4
+                    la.wait_stream(stream)
+                    with N_.cta_limits(half, 0):
+                        with torch.cuda.stream(la):
+                            launch_list[2][1](kt_ext, v_ext)        # grad_A
+                        launch_list[0][1](kt_ext, v_ext)            # window forward
+                    lb.wait_stream(stream)
+                    lc.wait_stream(la)
+                    with N_.cta_limits(quarter, 0):
+                        with torch.cuda.stream(lb):
+                            launch_list[3][1](kt_ext, v_ext)        # grad_V partial rows
+                        launch_list[1][1](kt_ext, v_ext)            # unwindow forward
+                        with torch.cuda.stream(lc):
+                            launch_list[5][1](kt_ext, v_ext)        # grad_K partial rows
+                        with torch.cuda.stream(la):
+                            launch_list[4][1](kt_ext, v_ext)        # grad_Q
+                    for x in (la, lb, lc):
+                        stream.wait_stream(x)
+                else:
+                    contractions(kt_ext, v_ext)
                 return ph.reduce()
             kt_ext, v_ext = halo([kt, v])   # views of the same storage every step: only the margins are written
             if graph is not None:
@@ -885,6 +933,8 @@ def measure_seq_sharded(args, torch, impl, N_, rank, world, dev, workload, steps
     peak, peak_kind = measured_peaks()
     result.update({
         "value_us": us, "n_gpus": world, "steps": steps, "workload": workload_name(workload), "rows_per_gpu": Ml,
+        "contractions": ("DAG, kernels of a level side by side on a share of the SMs each (wmm_set_cta_limits)" if seq_split
+                         else "one after the other, all SMs each"),
         "overlap": ("none: exchanges in stream order" if not (peer and side is not None) else
                     ("V exchange beside the window forward, grad_V / grad_K reductions beside the grad_K / grad_Q contractions"
                      if args.overlap == 1 else
@@ -956,10 +1006,14 @@ def main():
                     help="SMs a contraction leaves to the exchange that runs beside it (0: no caps)")
     ap.add_argument("--no-seq-extra", action="store_true", help="on several GPUs: skip the sequence-sharded config 4 step reported beside the headline")
     ap.add_argument("--tf32", action="store_true", help="fp32 workloads: multiply on the tensor cores as tf32 (WMM_FLAG_TF32) instead of the exact-order kernels")
+    ap.add_argument("--sm-split", default="auto",
+                    help="CTA caps for the five kernels of the step's DAG (window fwd, grad_A, unwindow fwd, grad_V, window bwd), "
+                         "'off', or 'auto': kernels of one level share the SMs when a GPU has fewer than 16 row tiles per SM")
     ap.add_argument("--branches", type=int, default=2, choices=[1, 2], help="capture the step as one chain (1) or with its real dependencies (2)")
     ap.add_argument("--no-graph", action="store_true", help="launch the six kernels on the stream instead of a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=0, help="override B of the workload (small cases for profiling)")
+    ap.add_argument("--rows", type=int, default=0, help="override M of the workload (e.g. the rows of a shard of a larger run)")
     ap.add_argument("--k-layout", default="view", choices=["view", "bnm"],
                     help="K as a transposed view of a (B,M,N) tensor (default) or as a contiguous (B,N,M) tensor")
     ap.add_argument("--shard", default="auto", choices=["auto", "batch", "seq"],
@@ -976,6 +1030,9 @@ def main():
     if args.batch > 0:
         B, M, N, w, dt, dist = WORKLOADS[args.workload]
         WORKLOADS[args.workload] = (args.batch, M, N, w, dt, dist)
+    if args.rows > 0:
+        B, M, N, w, dt, dist = WORKLOADS[args.workload]
+        WORKLOADS[args.workload] = (B, args.rows, N, w, dt, dist)
     if args.impl == "reference":
         run_reference(args, torch)
     elif args.impl == "reference_cuda":
