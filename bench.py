@@ -677,8 +677,9 @@ def _seq_parity(torch, impl, dev, workload, world, got, mine):
     """Rank 0's rows of all six results against the UNSHARDED kernels of this library on the same seeded rows: rows
     [0, Ml) of a sequence depend on positions below Ml + 2w only, so the plain operators run on rank 0's rows plus the
     first 2w rows of rank 1 (regenerated from rank 1's seed).  Returns, per tensor, max |x - y| / (1e-2 (|y| + rms(y)));
-    <= 1 means within the 16-bit bound.  The sharded grad_K / grad_V edge rows are sums of two rounded partial rows, so
-    they differ from the unsharded rows by a rounding, not bit for bit."""
+    <= 1 means within the 16-bit bound.  The sharded grad_K / grad_V edge rows are sums of two partial rows: summed from
+    this rank's unrounded fp32 rows and the neighbour's 16-bit rows (--edges 1) they carry one rounding more than the
+    unsharded rows; summed as 16-bit rows (--edges 0) two more, which can pass the bound where the partial rows cancel."""
     B, M, N, w, dt, distn = WORKLOADS[workload]
     dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[dt]
     Ml = M // world
@@ -746,7 +747,7 @@ def measure_seq_sharded(args, torch, impl, N_, rank, world, dev, workload, steps
     if peer:
         from window_matmul.peer_halo import PeerHalo
 
-        ph = PeerHalo(2, B, Ml, N, w, dtype, dev)
+        ph = PeerHalo(2, B, Ml, N, w, dtype, dev, edges=args.edges)
         ph.local(0).copy_(kt)
         ph.local(1).copy_(v)
 
@@ -755,10 +756,12 @@ def measure_seq_sharded(args, torch, impl, N_, rank, world, dev, workload, steps
         ("unwindow_fwd band_n", lambda k_, v_: impl.band_n(a, v_, w, other_off=off, seq=seq, out=o)),
         ("unwindow_bwd grad_A band_nt", lambda k_, v_: impl.band_nt(go, v_, w, other_off=off, seq=seq, out=ga)),
         ("unwindow_bwd grad_V band_t", lambda k_, v_: parts.__setitem__("gv", impl.band_t(
-            a, go, w, other_rows=ext, other_off=off, seq=seq, out=ph.partial(1) if peer else None))),
+            a, go, w, other_rows=ext, other_off=off, seq=seq, out=ph.partial(1) if peer else None,
+            edges=ph.edges(1) if peer else None, edge_skip=w))),
         ("window_bwd grad_Q band_n", lambda k_, v_: impl.band_n(ga, k_, w, other_off=off, seq=seq, out=gq)),
         ("window_bwd grad_K band_t", lambda k_, v_: parts.__setitem__("gk", impl.band_t(
-            ga, q, w, other_rows=ext, other_off=off, seq=seq, out=ph.partial(0) if peer else None))),
+            ga, q, w, other_rows=ext, other_off=off, seq=seq, out=ph.partial(0) if peer else None,
+            edges=ph.edges(0) if peer else None, edge_skip=w))),
     ]
 
     def contractions(kt_ext, v_ext):
@@ -933,6 +936,8 @@ def measure_seq_sharded(args, torch, impl, N_, rank, world, dev, workload, steps
     peak, peak_kind = measured_peaks()
     result.update({
         "value_us": us, "n_gpus": world, "steps": steps, "workload": workload_name(workload), "rows_per_gpu": Ml,
+        "partial_rows": ("own rows unrounded (fp32) until the neighbour's 16-bit rows are added (wmm_band_t_edges, wmm_halo_reduce_edges)"
+                         if (peer and ph is not None and ph.with_edges) else "summed as 16-bit rows"),
         "contractions": ("DAG, kernels of a level side by side on a share of the SMs each (wmm_set_cta_limits)" if seq_split
                          else "one after the other, all SMs each"),
         "overlap": ("none: exchanges in stream order" if not (peer and side is not None) else
@@ -1002,6 +1007,9 @@ def main():
                     help="sequence-sharded step: 0 = exchanges in stream order (default: fastest measured); 1 = the V exchange "
                          "and both reductions on a side stream beside contractions that do not need them; 2 = also the K^T "
                          "exchange, beside the window forward of the interior rows")
+    ap.add_argument("--edges", type=int, default=1, choices=[0, 1],
+                    help="sequence-sharded step: 1 = add the neighbour's partial grad_K / grad_V rows to this rank's unrounded fp32 "
+                         "rows; 0 = sum 16-bit rows (one rounding more)")
     ap.add_argument("--overlap-sms", type=int, default=8,
                     help="SMs a contraction leaves to the exchange that runs beside it (0: no caps)")
     ap.add_argument("--no-seq-extra", action="store_true", help="on several GPUs: skip the sequence-sharded config 4 step reported beside the headline")

@@ -261,6 +261,40 @@ WMM_API int wmm_halo_pull(const wmm_halo_buffer *buffers, int count, const wmm_h
 WMM_API int wmm_halo_pull_static(const wmm_halo_buffer *buffers, int count, const wmm_halo_flags *flags, int lane,
                                  int batch, int rows, int cols, int window, int dtype, int accumulate, void *stream);
 
+/* ---- sequence shards: partial grad_K / grad_V rows summed with one rounding less ------------------------------ */
+
+/* wmm_band_t for the 16-bit types that also writes output rows near both ends UNROUNDED, as fp32, into `edges`: a
+ * contiguous (batch, 2 * edge_rows, cols) buffer whose rows [0, edge_rows) stand for output rows [0, edge_rows) and
+ * whose rows [edge_rows, 2 * edge_rows) for output rows [other_rows - edge_rows, other_rows); the outermost `edge_skip`
+ * rows at each end are not written.  A sequence shard computes partial grad_K / grad_V rows for its margins and for its
+ * own rows next to them (edge_rows = 2 * window, edge_skip = window: the fp32 rows are its own first and last `window`
+ * rows); adding a neighbour's partial row to an own row that was already rounded to 16 bits costs a rounding the
+ * unsharded kernel does not have.  With the fp32 copy and wmm_halo_reduce_edges the own terms are not rounded before the
+ * sum.  Only the tensor-core kernels write edge rows: other dtypes and shapes fail with WMM_ERR_UNSUPPORTED; needs
+ * 2 * edge_rows <= other_rows, 0 <= edge_skip < edge_rows and `edges` 16-byte aligned.  No counterpart in the reference
+ * (it has no multi-GPU code). */
+WMM_API int wmm_band_t_edges(const void *band, const wmm_operand *x, const wmm_operand *out, float *edges, int edge_rows,
+                             int edge_skip, const wmm_geometry *g, int dtype, unsigned flags, void *stream);
+
+/* One tensor of wmm_halo_reduce_edges: `local` = this rank's extended (batch, rows + 2*window, cols) partial-row buffer
+ * of the 16-bit type (its own rows are the result), `mine` = the fp32 edge rows (batch, 4*window, cols) that
+ * wmm_band_t_edges wrote on this rank with edge_rows = 2*window, edge_skip = window, `lower` / `upper` = the neighbours'
+ * extended 16-bit buffers of the same tensor as in wmm_halo_buffer (peer pointers; NULL at an end of the sequence). */
+typedef struct wmm_halo_edges {
+  void *local;
+  const float *mine;
+  const void *lower;
+  const void *upper;
+} wmm_halo_edges;
+
+/* The reduction of wmm_halo_pull(accumulate != 0) with this rank's terms taken from its fp32 edge rows: its first
+ * `window` own rows <- round(its unrounded rows + the lower neighbour's upper-margin rows), its last `window` own rows
+ * likewise with the upper neighbour's lower-margin rows.  The neighbours' rows cross the link in 16 bits, as in
+ * wmm_halo_pull.  Same hand-shake, waits and status bit; WMM_F16 / WMM_BF16 only, cols a multiple of 8,
+ * rows >= 2*window. */
+WMM_API int wmm_halo_reduce_edges(const wmm_halo_edges *tensors, int count, const wmm_halo_flags *flags, int batch,
+                                  int rows, int cols, int window, int dtype, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

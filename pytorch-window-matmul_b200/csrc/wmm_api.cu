@@ -299,6 +299,35 @@ int wmm_halo_pull_static(const wmm_halo_buffer *buffers, int count, const wmm_ha
   return WMM_OK;
 }
 
+// The reduction of partial rows from unrounded fp32 edge rows (see include/wmm_b200.h).
+int wmm_halo_reduce_edges(const wmm_halo_edges *tensors, int count, const wmm_halo_flags *flags, int batch, int rows,
+                          int cols, int window, int dtype, void *stream) {
+  if (!tensors || !flags) return fail(WMM_ERR_NULL, "edge tensors or flags are NULL");
+  if (count < 1 || count > 4) return fail(WMM_ERR_SHAPE, "Input mismatch: 1 to 4 tensors per reduction, got %d", count);
+  if (dtype != WMM_F16 && dtype != WMM_BF16)
+    return fail(WMM_ERR_UNSUPPORTED, "edge rows exist for the 16-bit types only (dtype code %d)", dtype);
+  if (batch < 0 || rows < 0 || cols < 0 || window < 0)
+    return fail(WMM_ERR_SHAPE, "Input mismatch: negative extent (batch %d rows %d cols %d window %d)", batch, rows, cols, window);
+  if (rows < 2 * (int64_t)window)
+    return fail(WMM_ERR_SHAPE, "Input mismatch: a shard of %d rows is too short for window %d", rows, window);
+  if ((int64_t)batch * cols * window == 0) return WMM_OK;
+  if (cols % 8 != 0) return fail(WMM_ERR_STRIDE, "a row of %d elements is not a multiple of 16 bytes", cols);
+  if (!flags->mine || !flags->counters) return fail(WMM_ERR_NULL, "flag block or counters are NULL");
+  for (int i = 0; i < count; ++i) {
+    if (!tensors[i].local || !tensors[i].mine) return fail(WMM_ERR_NULL, "tensor %d has a NULL local pointer", i);
+    if (((uintptr_t)tensors[i].local | (uintptr_t)tensors[i].mine | (uintptr_t)tensors[i].lower | (uintptr_t)tensors[i].upper) & 15)
+      return fail(WMM_ERR_STRIDE, "tensor %d is not 16-byte aligned", i);
+    if ((tensors[i].lower != nullptr) != (flags->lower != nullptr) || (tensors[i].upper != nullptr) != (flags->upper != nullptr))
+      return fail(WMM_ERR_NULL, "tensor %d and the flags disagree on which neighbours exist", i);
+  }
+  int launches = 0;
+  cudaError_t err = wmm::launch_halo_pull(nullptr, count, *flags, flags->counters, flags->counters + 1, batch, rows, cols, window,
+                                          dtype, true, (cudaStream_t)stream, &launches, tensors);
+  g_launches.fetch_add((uint64_t)launches, std::memory_order_relaxed);
+  if (err != cudaSuccess) return fail(WMM_ERR_CUDA, "CUDA error launching the edge-row reduction: %s", cudaGetErrorString(err));
+  return WMM_OK;
+}
+
 uint64_t wmm_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int wmm_set_cta_limits(int contraction_ctas, int exchange_ctas) {
@@ -352,6 +381,24 @@ int wmm_band_t(const void *band, const wmm_operand *x, const wmm_operand *out, c
   wmm::Problem p{};
   const int s = build(wmm::BAND_T, p, x, nullptr, band, nullptr, out, g, dtype, flags);
   if (s != WMM_OK) return s < 0 ? s : WMM_OK;
+  return dispatch(wmm::BAND_T, p, stream);
+}
+
+int wmm_band_t_edges(const void *band, const wmm_operand *x, const wmm_operand *out, float *edges, int edge_rows,
+                     int edge_skip, const wmm_geometry *g, int dtype, unsigned flags, void *stream) {
+  wmm::Problem p{};
+  const int s = build(wmm::BAND_T, p, x, nullptr, band, nullptr, out, g, dtype, flags);
+  if (s != WMM_OK) return s < 0 ? s : WMM_OK;
+  if (!edges) return fail(WMM_ERR_NULL, "edges is NULL");
+  if ((uintptr_t)edges & 15) return fail(WMM_ERR_STRIDE, "edges is not 16-byte aligned");
+  if (edge_rows < 1 || 2 * (int64_t)edge_rows > g->other_rows || edge_skip < 0 || edge_skip >= edge_rows)
+    return fail(WMM_ERR_SHAPE, "Input mismatch: %d edge rows (the outer %d skipped) at each end do not fit %d output rows",
+                edge_rows, edge_skip, g->other_rows);
+  if ((dtype != WMM_F16 && dtype != WMM_BF16) || pick_family(wmm::BAND_T, p) != 1)
+    return fail(WMM_ERR_UNSUPPORTED, "only the tensor-core band_t of the 16-bit types writes edge rows");
+  p.edges = edges;
+  p.edge_rows = edge_rows;
+  p.edge_skip = edge_skip;
   return dispatch(wmm::BAND_T, p, stream);
 }
 

@@ -26,6 +26,10 @@ struct Problem {
   int64_t band_sb;         // elements between batch entries of the band (M * (2w+1) when contiguous)
   int32_t dtype;
   uint32_t flags;
+  // band_t on 16-bit types only: the first and the last `edge_rows` output rows (minus the outermost `edge_skip` at each
+  // end) once more, unrounded, as fp32 rows of a (B, 2 * edge_rows, N) contiguous buffer; NULL = none
+  float *edges;
+  int32_t edge_rows, edge_skip;
 };
 
 enum Primitive { BAND_NT = 1, BAND_N = 2, BAND_T = 3 };
@@ -54,7 +58,7 @@ cudaError_t launch_band_softmax(bool backward, const void *in, const void *in2, 
 // `epoch_word`: one local word counting the completed exchanges; `scratch`: three local words (CTAs done, go word per side).
 cudaError_t launch_halo_pull(const wmm_halo_buffer *bufs, int count, const wmm_halo_flags &flags, unsigned *epoch_word,
                              unsigned *scratch, int batch, int rows, int cols, int window, int dtype, bool accumulate,
-                             cudaStream_t stream, int *launches);
+                             cudaStream_t stream, int *launches, const wmm_halo_edges *edges = nullptr);
 
 // The same exchange with its scratch words in a static device array of the library (lane < WMM_HALO_STATIC_LANES) and
 // the exchange count in word 3 of flags.mine; no device memory is allocated.

@@ -51,6 +51,9 @@ struct HaloArgs {
   void *local[kHaloMaxBuffers];
   const void *lower[kHaloMaxBuffers];   // the lower neighbour's buffer of the same tensor (peer pointer) or NULL
   const void *upper[kHaloMaxBuffers];
+  // accumulate == 2 only: this rank's unrounded fp32 edge rows (B, 4w, cols) as band_t writes them with edge_rows = 2w,
+  // edge_skip = w: rows [w,2w) = first own rows, [2w,3w) = last own rows (the margins' rows of the buffer are not used)
+  const float *edge_mine[kHaloMaxBuffers];
   int count;
   int accumulate;
   int dtype;
@@ -147,6 +150,50 @@ __global__ void __launch_bounds__(THREADS, 1) halo_pull_kernel(const HaloArgs a)
   const long long per_side = (long long)a.count * per_buf;
   for (int side = 0; side < 2; ++side) {
     if (!ok_s[side]) continue;
+    if (a.accumulate == 2) {
+      // own edge rows = round(my UNROUNDED rows + the neighbour's margin rows): the neighbour's terms were rounded to 16
+      // bits once (they cross the link as such), mine not at all before the sum.  8 elements (one 16-byte vector) per
+      // item, 4 items per thread in flight.  Only the 16-bit types come here.
+      if constexpr (sizeof(T) == 2) {
+        constexpr int U = 4;
+        const long long strip_elems = a.strip_vecs * 8;
+        for (long long it0 = (long long)blockIdx.x * (THREADS * U) + threadIdx.x; it0 < per_side;
+             it0 += (long long)gridDim.x * (THREADS * U)) {
+          float4 mine[U][2];
+          uint4 theirs[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const long long it = it0 + (long long)u * THREADS;
+            if (it >= per_side) continue;
+            const int t = (int)(it / per_buf);
+            const long long q = it % per_buf;
+            const long long b = q / a.strip_vecs, v = q % a.strip_vecs;
+            const float *pm = a.edge_mine[t] + (b * 4 + (side == 0 ? 1 : 2)) * strip_elems + v * 8;
+            const uint4 *src = static_cast<const uint4 *>(side == 0 ? a.lower[t] : a.upper[t]);
+            theirs[u] = __ldcg(src + b * a.row_vecs + (side == 0 ? a.own_vecs : 0) + v);
+            mine[u][0] = *reinterpret_cast<const float4 *>(pm);
+            mine[u][1] = *(reinterpret_cast<const float4 *>(pm) + 1);
+          }
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const long long it = it0 + (long long)u * THREADS;
+            if (it >= per_side) continue;
+            const int t = (int)(it / per_buf);
+            const long long q = it % per_buf;
+            const long long b = q / a.strip_vecs, v = q % a.strip_vecs;
+            const long long d_off = b * a.row_vecs + (side == 0 ? a.strip_vecs : a.own_vecs - a.strip_vecs) + v;
+            uint4 out;
+            T *o = reinterpret_cast<T *>(&out);
+            const float *m = reinterpret_cast<const float *>(mine[u]);
+            const T *th = reinterpret_cast<const T *>(&theirs[u]);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) o[k] = ElemTraits<T>::store(m[k] + ElemTraits<T>::load(th + k));
+            static_cast<uint4 *>(a.local[t])[d_off] = out;
+          }
+        }
+      }
+      continue;
+    }
     // where item `it` comes from (in the neighbour's buffer) and goes to (in mine)
     auto place = [&](long long it, const uint4 *&src, uint4 *&dst) {
       const int t = (int)(it / per_buf);
@@ -219,16 +266,23 @@ __global__ void __launch_bounds__(THREADS, 1) halo_pull_kernel(const HaloArgs a)
 
 cudaError_t launch_halo_pull(const wmm_halo_buffer *bufs, int count, const wmm_halo_flags &flags, unsigned *epoch_word,
                              unsigned *scratch, int batch, int rows, int cols, int window, int dtype, bool accumulate,
-                             cudaStream_t stream, int *launches) {
+                             cudaStream_t stream, int *launches, const wmm_halo_edges *edges) {
   const size_t e = dtype == WMM_F32 ? 4 : dtype == WMM_F64 ? 8 : 2;
   HaloArgs a{};
   a.count = count;
   for (int i = 0; i < count; ++i) {
-    a.local[i] = bufs[i].local;
-    a.lower[i] = bufs[i].lower;
-    a.upper[i] = bufs[i].upper;
+    if (edges) {
+      a.local[i] = edges[i].local;
+      a.edge_mine[i] = edges[i].mine;
+      a.lower[i] = edges[i].lower;
+      a.upper[i] = edges[i].upper;
+    } else {
+      a.local[i] = bufs[i].local;
+      a.lower[i] = bufs[i].lower;
+      a.upper[i] = bufs[i].upper;
+    }
   }
-  a.accumulate = accumulate ? 1 : 0;
+  a.accumulate = edges ? 2 : accumulate ? 1 : 0;
   a.dtype = dtype;
   a.batch = batch;
   a.strip_vecs = (long long)window * cols * e / 16;

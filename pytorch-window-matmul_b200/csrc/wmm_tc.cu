@@ -361,6 +361,9 @@ template <bool BF16, int NH, int MODE, bool YMN> cudaError_t launch_mm(const Pro
   k.tiles_per_batch = (out_rows + TILE - 1) / TILE;
   k.total_tiles = k.tiles_per_batch * p.B;
   k.nchunks = (TILE + 2 * p.w + 127) / 128;
+  k.edges = MODE == 1 ? p.edges : nullptr;
+  k.edge_rows = MODE == 1 ? p.edge_rows : 0;
+  k.edge_skip = MODE == 1 ? p.edge_skip : 0;
   auto kern = band_mm_tc_kernel<BF16, NH, MODE, YMN>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::ALLOC);
   if (e != cudaSuccess) {

@@ -26,6 +26,11 @@ constexpr unsigned long long ST_MM_TIMEOUT = 1ull << 1;
 struct MmParams {
   int B, M, Mo, w, off, lo, hi;
   int tiles_per_batch, total_tiles, nchunks;
+  // band_t (MODE 1) only: unrounded fp32 copy of output rows [edge_skip, edge_rows) and [Mo - edge_rows, Mo - edge_skip)
+  // of every batch entry, at the same row index of a (B, 2 * edge_rows, NH) contiguous buffer (row Mo - edge_rows is its
+  // row edge_rows), for a sequence shard whose edge rows are summed with a neighbour's
+  float *edges;
+  int edge_rows, edge_skip;
 };
 
 template <int NH> struct MmSmem {
@@ -319,6 +324,15 @@ band_mm_tc_kernel(const __grid_constant__ CUtensorMap map_band, const __grid_con
         uint32_t v[32];
         tmem_ld_x32(taddr + g * 32, v);
         tmem_ld_wait();
+        if (MODE == 1 && p.edges != nullptr) {
+          const int e = t0 + rr;   // output row of this thread
+          const int er = e < p.edge_rows ? e : (e >= p.Mo - p.edge_rows && e < p.Mo ? e - (p.Mo - 2 * p.edge_rows) : -1);
+          if (er >= p.edge_skip && er < 2 * p.edge_rows - p.edge_skip) {
+            uint4 *dst = reinterpret_cast<uint4 *>(p.edges + ((size_t)b * 2 * p.edge_rows + er) * NH + g * 32);
+#pragma unroll
+            for (int q = 0; q < 8; q++) dst[q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+          }
+        }
 #pragma unroll
         for (int q4 = 0; q4 < 4; q4++) {
           const int col = g * 32 + q4 * 8;  // first hidden column of this 16-byte piece

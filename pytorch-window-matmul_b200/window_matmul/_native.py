@@ -53,6 +53,11 @@ class HaloBuffer(ctypes.Structure):
     _fields_ = [("local", ctypes.c_void_p), ("lower", ctypes.c_void_p), ("upper", ctypes.c_void_p)]
 
 
+class HaloEdges(ctypes.Structure):
+    """wmm_halo_edges of include/wmm_b200.h."""
+    _fields_ = [("local", ctypes.c_void_p), ("mine", ctypes.c_void_p), ("lower", ctypes.c_void_p), ("upper", ctypes.c_void_p)]
+
+
 class HaloFlags(ctypes.Structure):
     """wmm_halo_flags of include/wmm_b200.h."""
     _fields_ = [("mine", ctypes.c_void_p), ("lower", ctypes.c_void_p), ("upper", ctypes.c_void_p), ("counters", ctypes.c_void_p)]
@@ -95,6 +100,10 @@ def _load():
     lib.wmm_halo_pull.argtypes = [P(HaloBuffer), i32, P(HaloFlags), i32, i32, i32, i32, i32, i32, vp]
     lib.wmm_halo_pull_static.restype = i32
     lib.wmm_halo_pull_static.argtypes = [P(HaloBuffer), i32, P(HaloFlags), i32, i32, i32, i32, i32, i32, i32, vp]
+    lib.wmm_band_t_edges.restype = i32
+    lib.wmm_band_t_edges.argtypes = [vp, P(Operand), P(Operand), vp, i32, i32, P(Geometry), i32, u32, vp]
+    lib.wmm_halo_reduce_edges.restype = i32
+    lib.wmm_halo_reduce_edges.argtypes = [P(HaloEdges), i32, P(HaloFlags), i32, i32, i32, i32, i32, vp]
     lib.wmm_band_softmax.restype = i32
     lib.wmm_band_softmax.argtypes = [vp, vp, P(Geometry), i32, ctypes.c_float, u32, vp]
     lib.wmm_band_softmax_bwd.restype = i32

@@ -26,7 +26,7 @@ from . import _native as N
 
 
 class PeerHalo:
-    def __init__(self, count: int, batch: int, rows: int, cols: int, window: int, dtype, device, group=None):
+    def __init__(self, count: int, batch: int, rows: int, cols: int, window: int, dtype, device, group=None, edges=False):
         import torch.distributed._symmetric_memory as symm_mem
 
         if not 1 <= count <= 4:
@@ -44,6 +44,10 @@ class PeerHalo:
         self.flags = symm_mem.empty((64,), dtype=torch.int32, device=self.device)
         self.flags.zero_()
         self.counters = torch.zeros(4, dtype=torch.int32, device=self.device)
+        # optional: this rank's own first and last w rows of every partial gradient once more, unrounded (what
+        # band_t(..., edges=, edge_skip=w) writes), so that the reduction adds the neighbour's rows before any rounding
+        self.with_edges = bool(edges) and dtype in (torch.float16, torch.bfloat16)
+        self.edge_store = torch.zeros((count, batch, 4 * window, cols), dtype=torch.float32, device=self.device) if self.with_edges else None
         torch.cuda.synchronize(self.device)
         hdl = symm_mem.rendezvous(self.store, self.group)
         fhdl = symm_mem.rendezvous(self.flags, self.group)
@@ -66,6 +70,14 @@ class PeerHalo:
                 arr[i] = N.HaloBuffer(base(hdl, self.store, self.rank) + o, (base(hdl, self.store, lo) + o) if lo is not None else None,
                                       (base(hdl, self.store, hi) + o) if hi is not None else None)
             self._bufs.append(arr)
+        self._edges = None
+        if self.with_edges:
+            self._edges = (N.HaloEdges * count)()
+            for i in range(count):
+                o = (count + i) * per
+                self._edges[i] = N.HaloEdges(base(hdl, self.store, self.rank) + o, self.edge_store[i].data_ptr(),
+                                             (base(hdl, self.store, lo) + o) if lo is not None else None,
+                                             (base(hdl, self.store, hi) + o) if hi is not None else None)
         self._flags = N.HaloFlags(base(fhdl, self.flags, self.rank), base(fhdl, self.flags, lo) if lo is not None else None,
                                   base(fhdl, self.flags, hi) if hi is not None else None, self.counters.data_ptr())
         # in-sequence range of the extended row space of this rank (zeros stay in the margins at the global ends)
@@ -86,9 +98,22 @@ class PeerHalo:
         """Extended buffer for the partial gradient of operand i (what band_t writes with other_rows = rows + 2w)."""
         return self.store[self.count + i]
 
+    def edges(self, i: int):
+        """fp32 (batch, 4w, cols) buffer for the unrounded edge rows of partial gradient i (pass it to band_t with
+        edge_skip = window), or None."""
+        return self.edge_store[i] if self.with_edges else None
+
     def _pull(self, part: int, accumulate: bool, which=None) -> None:
         with torch.cuda.device(self.device):
             stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+            if accumulate and self.with_edges:
+                if which is None:
+                    eds, count = self._edges, self.count
+                else:
+                    eds, count = (N.HaloEdges * 1)(self._edges[which]), 1
+                N.check(N.lib.wmm_halo_reduce_edges(eds, count, ctypes.byref(self._flags), self.batch, self.rows, self.cols,
+                                                    self.window, N.dtype_code(self.store), stream))
+                return
             if which is None:
                 bufs, count = self._bufs[part], self.count
             else:   # one tensor only (every rank must then exchange the same one)

@@ -114,8 +114,10 @@ def band_n(band, y, window, *, rows_out=None, other_off=0, seq=None, out=None, f
     return o
 
 
-def band_t(band, x, window, *, other_rows=None, other_off=0, seq=None, out=None, flags=None):
-    """Out[b,p,:] = sum_i Band[b,i,p-other_off-i+w] X[b,i,:].  band (B,M,2w+1), x (B,M,N) -> (B,Mo,N)."""
+def band_t(band, x, window, *, other_rows=None, other_off=0, seq=None, out=None, flags=None, edges=None, edge_skip=0):
+    """Out[b,p,:] = sum_i Band[b,i,p-other_off-i+w] X[b,i,:].  band (B,M,2w+1), x (B,M,N) -> (B,Mo,N).
+    `edges`: a contiguous fp32 (B, 2r, N) tensor that receives the first and the last r output rows unrounded, minus
+    the outermost `edge_skip` rows at each end (wmm_band_t_edges; 16-bit types on the tensor-core kernels only)."""
     _require_cuda(band, x)
     (band, band_sb), x = _band_in(band), _addressable(x)
     B, M, W = band.shape
@@ -124,9 +126,17 @@ def band_t(band, x, window, *, other_rows=None, other_off=0, seq=None, out=None,
     Mo = M if other_rows is None else other_rows
     o = torch.empty((B, Mo, Nn), dtype=x.dtype, device=x.device) if out is None else _check_out(out, (B, Mo, Nn), x, False)
     g = N.geometry(B, M, Nn, window, Mo, other_off, seq, band_sb)
+    if edges is not None:
+        _mismatch(edges.dim() == 3 and edges.shape[0] == B and edges.shape[2] == Nn and edges.shape[1] % 2 == 0
+                  and 0 < edges.shape[1] <= Mo and edges.dtype == torch.float32 and edges.device == x.device
+                  and edges.is_contiguous() and edges.data_ptr() % 16 == 0)
     with torch.cuda.device(x.device):
-        N.check(N.lib.wmm_band_t(band.data_ptr(), N.operand(x), N.operand(o), g, N.dtype_code(x),
-                                 _FLAGS if flags is None else flags, N.stream_of(x)))
+        if edges is not None:
+            N.check(N.lib.wmm_band_t_edges(band.data_ptr(), N.operand(x), N.operand(o), edges.data_ptr(), edges.shape[1] // 2, int(edge_skip), g,
+                                           N.dtype_code(x), _FLAGS if flags is None else flags, N.stream_of(x)))
+        else:
+            N.check(N.lib.wmm_band_t(band.data_ptr(), N.operand(x), N.operand(o), g, N.dtype_code(x),
+                                     _FLAGS if flags is None else flags, N.stream_of(x)))
     return o
 
 

@@ -41,6 +41,29 @@ def test_cta_limits_are_validated_and_reset():
     assert N.lib.wmm_set_cta_limits(0, 0) == 0
 
 
+def test_edge_row_entry_points_validate_without_a_gpu():
+    import ctypes as C
+
+    from window_matmul import _native as N
+
+    g = N.geometry(2, 256, 64, 64, 384, 64, (0, 384), 0)
+    x = N.Operand(4096, 256 * 64, 64, 1)
+    o = N.Operand(8192, 384 * 64, 64, 1)
+    # (status, message): NULL edges, misaligned, too many rows, wrong dtype
+    assert N.lib.wmm_band_t_edges(1024, C.byref(x), C.byref(o), None, 128, 64, g, N.BF16, 0, None) == -1
+    assert N.lib.wmm_band_t_edges(1024, C.byref(x), C.byref(o), 4100, 128, 64, g, N.BF16, 0, None) == -4
+    assert N.lib.wmm_band_t_edges(1024, C.byref(x), C.byref(o), 4096, 200, 0, g, N.BF16, 0, None) == -2
+    assert N.lib.wmm_band_t_edges(1024, C.byref(x), C.byref(o), 4096, 128, 128, g, N.BF16, 0, None) == -2   # nothing left to write
+    assert N.lib.wmm_band_t_edges(1024, C.byref(x), C.byref(o), 4096, 128, 64, g, N.F32, 0, None) == -7
+    assert b"edge rows" in N.lib.wmm_last_error_string()
+    e = (N.HaloEdges * 1)(N.HaloEdges(256, 512, 768, 1024))
+    fl = N.HaloFlags(2048, 4096, 8192, 16384)
+    assert N.lib.wmm_halo_reduce_edges(e, 1, C.byref(fl), 2, 256, 64, 64, N.F32, None) == -7
+    assert N.lib.wmm_halo_reduce_edges(e, 1, C.byref(fl), 2, 100, 64, 64, N.BF16, None) == -2      # shard shorter than 2w
+    assert N.lib.wmm_halo_reduce_edges(e, 1, C.byref(fl), 2, 256, 60, 64, N.BF16, None) == -4      # row not a multiple of 16 B
+    assert N.lib.wmm_halo_reduce_edges(e, 1, C.byref(fl), 0, 256, 64, 64, N.BF16, None) == 0       # nothing to do
+
+
 def test_argument_validation_needs_no_gpu():
     from window_matmul import _native as N
 

@@ -265,6 +265,64 @@ def test_exchange_under_a_cta_limit_moves_the_same_bytes(accumulate):
     assert not torch.equal(results[0].cpu(), start)
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype,Nn", [(torch.bfloat16, 64), (torch.float16, 128)])
+def test_edge_rows_of_band_t_and_their_reduction(dtype, Nn):
+    """wmm_band_t_edges writes output rows near both ends once more as unrounded fp32 (here, as a sequence shard does, the
+    first and last w OWN rows: edge_rows = 2w, edge_skip = w); wmm_halo_reduce_edges adds the neighbours' 16-bit margin rows
+    to those and rounds once.  ONE GPU: the rank is its own two neighbours, so its first w own rows receive its own upper
+    margin and its last w own rows its own lower margin."""
+    import ctypes as C
+    import importlib
+
+    sys.path[:0] = [ROOT, os.path.join(ROOT, "pytorch-window-matmul_b200")]
+    from window_matmul import _native as N
+
+    impl = importlib.import_module("window_matmul.window_matmul")
+    dev = torch.device("cuda", 0)
+    B, Ml, w = 3, 768, 128
+    ext = Ml + 2 * w
+    g = torch.Generator().manual_seed(5)
+    band = (torch.randn(B, Ml, 2 * w + 1, generator=g) / 4).to(dtype).to(dev)
+    x = torch.randn(B, Ml, Nn, generator=g).to(dtype).to(dev)
+    flags = N.FLAG_REQUIRE_TENSOR
+    plain = impl.band_t(band, x, w, other_rows=ext, other_off=w, flags=flags)
+    edges = torch.full((B, 4 * w, Nn), float("nan"), dtype=torch.float32, device=dev)
+    out = impl.band_t(band, x, w, other_rows=ext, other_off=w, flags=flags, edges=edges, edge_skip=w)
+    torch.cuda.synchronize()
+    assert torch.equal(out, plain)                                        # the 16-bit output does not change
+    assert torch.isnan(edges[:, :w]).all() and torch.isnan(edges[:, 3 * w:]).all()   # the skipped rows are not written
+    own = edges[:, w:3 * w]
+    assert torch.equal(own.to(dtype), torch.cat([out[:, w:2 * w], out[:, ext - 2 * w:ext - w]], dim=1))   # the same sums ...
+    assert (own != own.to(dtype).float()).float().mean() > 0.5                                            # ... not rounded
+    # all 2w rows at each end with edge_skip = 0
+    full = torch.empty_like(edges)
+    impl.band_t(band, x, w, other_rows=ext, other_off=w, flags=flags, edges=full)
+    assert torch.equal(full.to(dtype), torch.cat([out[:, :2 * w], out[:, ext - 2 * w:]], dim=1))
+    assert torch.equal(full[:, w:3 * w], own)
+    # reduction on a self-ring: own first w rows += own upper margin, own last w rows += own lower margin
+    fl = torch.zeros(4, dtype=torch.int32, device=dev)
+    counters = torch.zeros(4, dtype=torch.int32, device=dev)
+    arr = (N.HaloEdges * 1)(N.HaloEdges(out.data_ptr(), edges.data_ptr(), out.data_ptr(), out.data_ptr()))
+    hf = N.HaloFlags(fl.data_ptr(), fl.data_ptr(), fl.data_ptr(), counters.data_ptr())
+    want = out.clone()
+    want[:, w:2 * w] = (edges[:, w:2 * w] + out[:, ext - w:].float()).to(dtype)
+    want[:, Ml:Ml + w] = (edges[:, 2 * w:3 * w] + out[:, :w].float()).to(dtype)
+    stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    N.check(N.lib.wmm_halo_reduce_edges(arr, 1, C.byref(hf), B, Ml, Nn, w, N.dtype_code(out), stream))
+    torch.cuda.synchronize()
+    assert N.device_status() == 0 and int(fl[0]) == 1
+    assert torch.equal(out, want)
+    # what it buys: against the sum of the unrounded terms, the 16-bit sum is further off
+    exact = full[:, w:2 * w].double() + full[:, 3 * w:].double()
+    with_edges = (out[:, w:2 * w].double() - exact).abs().max()
+    as_16bit = ((plain[:, w:2 * w].float() + plain[:, ext - w:].float()).to(dtype).double() - exact).abs().max()
+    assert with_edges <= as_16bit
+    # other kernel families have no edge rows
+    with pytest.raises(RuntimeError, match="edge rows"):
+        impl.band_t(band.float(), x.float(), w, other_rows=ext, other_off=w, edges=edges)
+
+
 def _peer_chain_worker(rank, world, port, shape, dtype_name, out_dir):
     import importlib
 
