@@ -897,13 +897,18 @@ def measure_seq_sharded(args, torch, impl, N_, rank, world, dev, workload, steps
                 step()
             stream.synchronize()
         barrier()
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        # five blocks of `steps` steps each, every block between two events; the MEDIAN block counts (a step is half a
+        # millisecond and the ranks meet in every exchange: one late rank stretches a whole block)
+        nblk = 5
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(nblk)]
         with ClockSampler(dev.index) as clocks:
-            ev0.record(stream)
-            for _ in range(steps):
-                step()
-            ev1.record(stream)
+            for b0, b1 in evs:
+                b0.record(stream)
+                for _ in range(steps):
+                    step()
+                b1.record(stream)
             stream.synchronize()
+        block_ms = sorted(b0.elapsed_time(b1) for b0, b1 in evs)
         barrier()
 
         # ---- per-launch durations: every rank issues the same launch, `reps` times, between two barriers ----
@@ -928,10 +933,13 @@ def measure_seq_sharded(args, torch, impl, N_, rank, world, dev, workload, steps
             per_launch.append(k0.elapsed_time(k1) * 1e3 / reps)
         barrier()
     status = N_.device_status()
-    t = torch.tensor([ev0.elapsed_time(ev1), float(status)] + per_launch, dtype=torch.float64, device=dev)
+    t = torch.tensor([block_ms[nblk // 2], float(status)] + per_launch + [block_ms[0], block_ms[-1]], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     us = float(t[0]) * 1e3 / steps
+    blocks_us = {"n": nblk, "steps_each": steps, "value_is": "median block, max over ranks",
+                 "min_us": round(float(t[-2]) * 1e3 / steps, 1), "max_us": round(float(t[-1]) * 1e3 / steps, 1)}
+    t = t[:-2]
     total_bytes, total_flops = algorithmic(B, M, N, w, e)
     peak, peak_kind = measured_peaks()
     result.update({
@@ -951,6 +959,7 @@ def measure_seq_sharded(args, torch, impl, N_, rank, world, dev, workload, steps
         "launch": ("stream launches" if graph is None else "one cuda graph per step (exchanges and contractions)" if peer
                    else "cuda graph of the six contractions between two NCCL exchanges"),
         "launches_per_step": int(launches_per_step),
+        "blocks": blocks_us,
         "per_launch_us_max_over_ranks": {name: round(float(x), 1) for (name, _), x in zip(seq_launches, t[2:].tolist())},
         "alg_MB": round(total_bytes / 1e6, 1),
         "frac_of_%s_hbm" % peak_kind: round(total_bytes / world / (us * 1e-6) / 1e9 / peak, 4),
@@ -985,7 +994,7 @@ def run_seq_sharded(args, torch, impl, N_, rank, world, dev):
                               "achieved_GBps": round(total_bytes / (us * 1e-6) / 1e9, 1),
                               **{k: v for k, v in r.items() if k.startswith("frac_of_")}},
             "per_launch_us_max_over_ranks": r["per_launch_us_max_over_ranks"], "parity_vs_unsharded": r.get("parity"),
-            "gpu_launches": int(r["launches_per_step"] * args.steps), "clocks": r["clocks"],
+            "gpu_launches": int(r["launches_per_step"] * args.steps * r["blocks"]["n"]), "clocks": r["clocks"],
         }
         print(json.dumps(line), flush=True)
     if world > 1:
