@@ -554,8 +554,10 @@ def run_ours(args, torch):
             return out.detach(), qd_.grad, ktd_.grad, vd_.grad
 
         # a handful of chunks: enough for uploads, kernels and downloads to overlap, few enough that the host-side cost
-        # per chunk (autograd, ~10 launches) stays small against the copies
-        e2e_chunks = args.e2e_chunks if args.e2e_chunks > 0 else max(3, min(8, Bl // 12))
+        # per chunk (autograd, ~10 launches: ~0.45 ms measured) stays below the copies of a chunk (12 sequences = 25 MB each
+        # way = ~0.5 ms): one chunk per 12 sequences, at most 8 (12 sequences per GPU: 1.09 / 1.29 / 1.72 / 2.18 ms with
+        # 1 / 2 / 3 / 4 chunks)
+        e2e_chunks = args.e2e_chunks if args.e2e_chunks > 0 else max(1, min(8, Bl // 12))
 
         def e2e_step():
             # host tensors in, host tensors out; uploads, kernels and downloads of batch chunks overlap
